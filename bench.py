@@ -1,0 +1,397 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A16 hot path (INT4 unpack + dequant fused into GEMV / GEMM) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload sweep|...]
+
+One JSON line on stdout (rank 0).  Workload `sweep` (default) is the batched GEMV / small-GEMM
+sweep: M in {1,4,8,16,64} x (K,N) in {(4096,4096),(4096,14336),(14336,4096)}, group 128,
+asymmetric uint4 zeros, bf16 activations and output.  A step is one pass over the 15 linears,
+each on its own weight copy (335 MB touched per step, so every weight byte comes from HBM).
+With N > 1 ranks every linear is column-parallel (N/ranks output columns per GPU) followed by an
+NCCL all-gather of the outputs: total work is fixed, i.e. strong scaling.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GROUP = 128
+SWEEP_SHAPES = [(4096, 4096), (4096, 14336), (14336, 4096)]
+SWEEP_MS = [1, 4, 8, 16, 64]
+
+
+def algo_bytes(M, K, N, out_bytes=2, zeros=True, group=GROUP):
+    """Algorithmic bytes of one linear: codes + scales + zeros + X + Y (scratch and re-reads do not count)."""
+    G = K // group
+    return K * N // 2 + G * N * 2 + (G * N // 2 if zeros else 0) + M * K * 2 + M * N * out_bytes
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.lines = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # samples under load = upper half (the sampler also sees idle moments at both ends)
+        sm_sorted = sorted(sm)
+        under_load = sm_sorted[len(sm_sorted) // 2:]
+        return {"sm_mhz": statistics.median(under_load), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm (the oracle's C port, timed on the host cores): cpu_baseline leg and --impl reference
+# ------------------------------------------------------------------------------------------------
+def cpu_sweep_sample(budget_s: float, cases):
+    """Times the C port of the reference arithmetic on `cases` until `budget_s` is used up.
+
+    Returns (bytes_done, seconds, n_cases_done, threads).
+    """
+    import numpy as np
+    from oracle import c_oracle, qf_oracle as O
+
+    threads = c_oracle.num_threads()
+    done_bytes, elapsed, n_done = 0, 0.0, 0
+    cache = {}
+    for (M, K, N) in cases:
+        if elapsed >= budget_s and n_done > 0:
+            break
+        if (K, N) not in cache:
+            rng = np.random.default_rng(K * 7 + N)
+            qw = rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)
+            sc = np.maximum(np.abs(rng.normal(0, 0.02, size=(K // GROUP, N))) / 7.0, 2.0 ** -14).astype(np.float32)
+            sc16 = c_oracle.to_bits(O.round_to(sc, "bf16"), "bf16")
+            zw = rng.integers(0, 2 ** 32, size=(K // GROUP, N // 8), dtype=np.uint32)
+            cache = {(K, N): (qw, sc16, zw)}  # keep one shape resident at a time
+        qw, sc16, zw = cache[(K, N)]
+        x16 = c_oracle.to_bits(O.round_to(np.random.default_rng(M).normal(size=(M, K)).astype(np.float32), "bf16"),
+                               "bf16")
+        t0 = time.perf_counter()
+        c_oracle.w4a16_linear(x16, qw, sc16, zw, GROUP, "bf16", "bf16")
+        elapsed += time.perf_counter() - t0
+        done_bytes += algo_bytes(M, K, N)
+        n_done += 1
+    return done_bytes, elapsed, n_done, threads
+
+
+def sweep_cases():
+    return [(M, K, N) for (K, N) in SWEEP_SHAPES for M in SWEEP_MS]
+
+
+def run_reference_arm(args):
+    """The reference's arithmetic on the host cores (C port of the oracle; the reference itself ships no
+    runnable lowering and its Python script needs the reference checkout, which is absent on the GPU box)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import c_oracle
+    c_oracle.lib()
+    cases = sweep_cases()
+    # bounded sample per step: the three M=1 linears (one per shape)
+    sample = [(1, K, N) for (K, N) in SWEEP_SHAPES]
+    for _ in range(args.warmup):
+        cpu_sweep_sample(1e9, sample[:1])
+    total_b, total_s = 0, 0.0
+    for _ in range(args.steps):
+        b, s, _, threads = cpu_sweep_sample(1e9, sample)
+        total_b += b
+        total_s += s
+    gbs = total_b / total_s / 1e9
+    full_bytes = sum(algo_bytes(*c) for c in cases)
+    line = {
+        "impl": "reference", "metric": "w4a16_linear_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": (full_bytes / (gbs * 1e9)) * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "cfg1_sweep", "group_size": GROUP, "zeros": "uint4 per (group,n)",
+                   "note": "ms_per_step = full 15-linear sweep at the sampled rate"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": "M=1 linears of the three sweep shapes per step"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="sweep", choices=["sweep"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import quantforge_b200 as qf
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the product has no CPU path)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    pk = peaks()
+
+    # ---- inputs: 5 weight copies per shape (one per M), column shard of this rank ----
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+    cases = []
+    for (K, N) in SWEEP_SHAPES:
+        assert N % world == 0
+        Nl = N // world
+        G = K // GROUP
+        for M in SWEEP_MS:
+            qw = torch.randint(-128, 128, (Nl, K // 2), dtype=torch.int8, device=dev, generator=gen)
+            sc = (torch.randn(G, Nl, device=dev, generator=gen).abs() * (0.02 / 7.0)).clamp_min(2.0 ** -14).to(
+                torch.bfloat16)
+            zr = qf.pack_zeros_u4(torch.randint(0, 16, (G, Nl), dtype=torch.int8, device=dev, generator=gen))
+            x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+            y = torch.empty(M, Nl, dtype=torch.bfloat16, device=dev)
+            yg = torch.empty(world, M, Nl, dtype=torch.bfloat16, device=dev) if world > 1 else None
+            cases.append({"M": M, "K": K, "N": N, "Nl": Nl, "qw": qw, "sc": sc, "zr": zr, "x": x, "y": y, "yg": yg,
+                          "x_host": x.cpu().pin_memory(), "y_host": torch.empty(M, Nl, dtype=torch.bfloat16).pin_memory()})
+    total_bytes = sum(algo_bytes(c["M"], c["K"], c["N"]) for c in cases)  # whole job, all ranks
+
+    def launch(c):
+        qf.w4a16_linear(c["x"], c["qw"], c["sc"], c["zr"], group_size=GROUP, out=c["y"])
+        if world > 1:
+            dist.all_gather_into_tensor(c["yg"], c["y"])
+
+    def one_step(subset=None):
+        for c in (subset if subset is not None else cases):
+            launch(c)
+
+    def make_graph(subset=None):
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(3):
+                one_step(subset)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            one_step(subset)
+        return g
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def time_graph(g, steps, warmup):
+        for _ in range(warmup):
+            g.replay()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            g.replay()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    # ---- main timed region: K replays of the step graph ----
+    g_step = make_graph()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches_before = qf.launch_count()
+    ms_total = time_graph(g_step, args.steps, args.warmup)
+    launches = (len(cases)) * args.steps  # graph replays do not pass through the host launch counter
+    host_launches = qf.launch_count() - launches_before
+    # keep the identical load running so that the 100 ms clock sampler sees it
+    t_end = time.time() + 1.5
+    while time.time() < t_end:
+        for _ in range(50):
+            g_step.replay()
+        torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = ms_total / args.steps
+    value = total_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- roofline of the dominant kernel: the GEMV kernel (M <= 8 cases), timed alone ----
+    gemv_cases = [c for c in cases if c["M"] <= 8]
+    gemm_cases = [c for c in cases if c["M"] > 8]
+    roof = {}
+    for name, sub in (("gemv", gemv_cases), ("gemm", gemm_cases)):
+        # two different shape orders per replay so consecutive launches never share weights
+        g = make_graph(sub)
+        ms = time_graph(g, max(args.steps, 20), args.warmup)
+        per_launch_s = ms / max(args.steps, 20) / len(sub) * 1e-3
+        b = sum(algo_bytes(c["M"], c["K"], c["N"]) for c in sub) / len(sub) / world
+        roof[name] = {"avg_us": per_launch_s * 1e6, "achieved": b / per_launch_s / 1e9, "bytes_per_launch": b}
+    dom = "gemv"
+    roofline = {"bound": "hbm", "kernel": "qf::gemv_kernel", "achieved": roof[dom]["achieved"],
+                "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": roof[dom]["achieved"] / pk["hbm_gbs"],
+                "traffic": None, "peak_source": pk["source"], "avg_launch_us": roof[dom]["avg_us"],
+                "algorithmic_bytes_per_launch": roof[dom]["bytes_per_launch"],
+                "other_kernels": {"gemm_m16_m64": {"achieved": roof["gemm"]["achieved"],
+                                                   "frac": roof["gemm"]["achieved"] / pk["hbm_gbs"],
+                                                   "avg_launch_us": roof["gemm"]["avg_us"]}}}
+
+    # ---- end to end: host activations in, host result out, through the public API ----
+    def e2e_step():
+        for c in cases:
+            qf.w4a16_linear_host(c["x_host"], c["qw"], c["sc"], c["zr"], group_size=GROUP, out_host=c["y_host"])
+    e2e_steps = max(3, min(args.steps, 50))
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    h2d = sum(c["M"] * c["K"] * 2 for c in cases)
+    d2h = sum(c["M"] * c["Nl"] * 2 for c in cases)
+    e2e = {"value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
+           "note": "activations from pinned host memory and results back to host every call; weights resident"}
+
+    # ---- per-case detail (device time, each case in its own graph of 8 weight-rotating launches) ----
+    detail = []
+    if not args.no_extras and world == 1:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        for c in cases:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ts = []
+            for it in range(12):
+                flush.fill_(it)
+                e0.record()
+                launch(c)
+                e1.record()
+                torch.cuda.synchronize()
+                if it >= 2:
+                    ts.append(e0.elapsed_time(e1) * 1e3)
+            us = statistics.median(ts)
+            b = algo_bytes(c["M"], c["K"], c["N"])
+            detail.append({"M": c["M"], "K": c["K"], "N": c["N"], "us": round(us, 2),
+                           "gbs": round(b / us / 1e3, 1), "frac_hbm": round(b / us / 1e3 / pk["hbm_gbs"], 3)})
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        b, s, n_done, threads = cpu_sweep_sample(20.0, sweep_cases())
+        cpu_baseline = {"value": b / s / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+                        "sample": f"first {n_done} of the 15 sweep linears, once each ({s:.1f} s of CPU time)"}
+
+    if rank == 0:
+        line = {
+            "metric": "w4a16_linear_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "cfg1_sweep", "cases": "M in {1,4,8,16,64} x (K,N) in {(4096,4096),(4096,14336),(14336,4096)}",
+                       "group_size": GROUP, "zeros": "uint4 per (group,n)", "out_dtype": "bf16",
+                       "parallelism": "single GPU" if world == 1 else f"column-parallel x{world} + NCCL all-gather",
+                       "l2": "inputs larger than L2: 15 weight copies, 335 MB touched per step",
+                       "timing": "CUDA graph of one step replayed K times between CUDA events",
+                       "clock_sampling": "timed region plus 1.5 s of the identical replay load"},
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
+            "host_side_launch_calls_in_timed_region": host_launches, "clocks": clocks,
+        }
+        if detail:
+            line["cases"] = detail
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

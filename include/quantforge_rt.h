@@ -1,0 +1,130 @@
+/*
+ * quantforge_rt.h - C ABI of the B200 (sm_100a) runtime for QuantForge's W4A16 hot path.
+ *
+ * The QuantForge reference is an MLIR dialect (ops qf.unpack, qf.dequant) plus passes that
+ * lower those ops to arithmetic; it ships no runtime.  This library is the runtime those ops
+ * lower INTO: each entry point below replaces the lowering (or the PyTorch statement) of one
+ * reference op, cited beside it by its path inside the reference project.
+ *
+ * Conventions
+ *   - every function returns a qf_status (0 = QF_OK, negative = error); no exception crosses the ABI;
+ *   - the caller owns every buffer; pointers are DEVICE pointers unless a name ends in `_host`;
+ *     device buffers must be 16-byte aligned;
+ *   - launches are asynchronous on the `stream` argument (a cudaStream_t passed as void*; NULL = default stream);
+ *   - the hot calls allocate nothing: split-K scratch comes from the caller (`workspace`);
+ *   - there is no CPU fallback: without a CUDA device every compute call returns QF_ERR_CUDA.
+ *
+ * Canonical tensor layouts for a linear Y[M,N] = X[M,K] . W^T, group size g, G = K/g
+ *   qweight  int8[N, K/2] == little-endian uint32[N, K/8]; nibble i of word j of row n is code q[n, 8j+i]
+ *   scales   f16|bf16 [G, N]   (same 16-bit type as the activations)
+ *   qzeros   QF_ZERO_U4 : uint32[G, N/8], 8 four-bit codes per word along N, LSB first
+ *            QF_ZERO_I8 : int8[G, N] (signed, the dialect's zero_point element type)
+ *            QF_ZERO_CONST : no tensor, the value desc.zero_const
+ *   X        f16|bf16 [M, K] row-major,  Y f16|bf16|f32 [M, N] row-major
+ */
+#ifndef QUANTFORGE_RT_H
+#define QUANTFORGE_RT_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QF_RT_VERSION 100 /* major*10000 + minor*100 + patch */
+
+typedef enum qf_status {
+    QF_OK = 0,
+    QF_ERR_BAD_ARG = -1,       /* null / misaligned pointer, shape not a multiple of the tile */
+    QF_ERR_UNSUPPORTED = -2,   /* valid request the kernels do not cover (e.g. group size) */
+    QF_ERR_CUDA = -3,          /* a CUDA runtime/driver call failed; see qf_last_error */
+    QF_ERR_NCCL = -4,
+    QF_ERR_TIMEOUT = -5,       /* a bounded device-side wait expired */
+    QF_ERR_UNIMPLEMENTED = -6,
+    QF_ERR_WORKSPACE = -7      /* workspace missing or smaller than qf_w4a16_workspace_bytes */
+} qf_status;
+
+typedef enum qf_dtype { QF_F16 = 0, QF_BF16 = 1, QF_F32 = 2 } qf_dtype;
+typedef enum qf_zero_mode { QF_ZERO_CONST = 0, QF_ZERO_U4 = 1, QF_ZERO_I8 = 2 } qf_zero_mode;
+
+/* Which kernel family serves a linear.  AUTO: M <= 8 -> GEMV kernel, M >= 9 -> tcgen05 GEMM kernel. */
+typedef enum qf_path { QF_PATH_AUTO = 0, QF_PATH_GEMV = 1, QF_PATH_GEMM = 2 } qf_path;
+
+typedef struct qf_ctx qf_ctx;
+
+typedef struct qf_linear_desc {
+    int64_t M, N, K;
+    int32_t group_size;  /* multiple of 128 dividing K (K itself = per-output-channel) */
+    int32_t act_dtype;   /* qf_dtype of X and of scales: QF_F16 or QF_BF16 */
+    int32_t out_dtype;   /* qf_dtype of Y */
+    int32_t zero_mode;   /* qf_zero_mode */
+    int32_t zero_const;  /* used when zero_mode == QF_ZERO_CONST (8 = symmetric int4, 0 = the zp==0 fast path) */
+    int32_t path;        /* qf_path */
+    int32_t split_k;     /* 0 = heuristic; >0 forces the number of K splits */
+    int32_t reserved[5]; /* must be zero */
+} qf_linear_desc;
+
+int qf_version(void);
+const char *qf_status_string(int status);
+
+/* One context per device. Owns only small caches (tensor maps, staging buffers of the *_host calls). */
+int qf_ctx_create(qf_ctx **out, int device);
+int qf_ctx_destroy(qf_ctx *ctx);
+/* Message of the last error recorded on this context (never NULL). */
+const char *qf_last_error(const qf_ctx *ctx);
+
+/*
+ * qf.unpack  (include/QuantForge/Dialect/QuantForge/QuantForgeOps.td:18-42; arithmetic:
+ * lib/Transforms/LowerUnpackToArith.cpp:173-214, word order lib/Transforms/LowerUnpackToNVVM.cpp:221-280;
+ * python/quantforge/baseline.py:34-49 `unpack_int4`).
+ * packed int8[rows, packed_cols] -> out int8[rows, 2*packed_cols]:
+ * out[r, 2i] = b & 0xF, out[r, 2i+1] = (b >>logical 4) & 0xF.  Bit-exact.
+ */
+int qf_unpack_int4(qf_ctx *ctx, const void *packed_i8, void *out_i8, int64_t rows, int64_t packed_cols, void *stream);
+
+/*
+ * qf.dequant(qf.unpack(w))  materialised (the fused elementwise op of
+ * lib/Transforms/FuseUnpackDequant.cpp:209-304; dequant arithmetic
+ * lib/Transforms/LowerDequantToArith.cpp:141-159; zp==0 path
+ * lib/Transforms/CanonicalizeDequantZeroPoint.cpp:177-192).
+ * W[n,k] = round_act((q[n,k] - z[k/g,n]) * s[k/g,n]) written as act_dtype [N,K].
+ * Uses N, K, group_size, act_dtype, zero_mode, zero_const of `desc`.  The linear below never
+ * materialises W; this entry point exists because the reference op does and to make the
+ * in-register conversion testable bit for bit.
+ */
+int qf_dequant_w4(qf_ctx *ctx, const qf_linear_desc *desc, const void *qweight, const void *scales,
+                  const void *qzeros_or_null, void *w_out, void *stream);
+
+/*
+ * linalg.matmul(x, qf.dequant(qf.unpack(w), scale, zp))  as one call
+ * (matcher lib/Transforms/ConvertLinalgToQuantForge.cpp:63-209, contraction :185-203;
+ * python/quantforge/baseline.py:52-72 `gemv_int4_baseline`).
+ * fp32 accumulation.  `workspace` must hold qf_w4a16_workspace_bytes(desc) bytes, be zero-filled
+ * once before its first use, and not be shared by calls that overlap in time; the kernels leave
+ * it ready for the next call.  It may be NULL when the size is 0.
+ */
+size_t qf_w4a16_workspace_bytes(const qf_linear_desc *desc);
+int qf_w4a16_linear(qf_ctx *ctx, const qf_linear_desc *desc, const void *X, const void *qweight, const void *scales,
+                    const void *qzeros_or_null, void *Y, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * The same linear for callers that hold activations in HOST memory (the reference's Python entry
+ * point takes CPU tensors when no GPU is used): copies X_host to the device, runs the kernel,
+ * copies Y back and waits.  Weights, scales and zeros stay DEVICE pointers (they are loaded once).
+ * Staging buffers live in the context and grow on first use; workspace as above.
+ */
+int qf_w4a16_linear_host(qf_ctx *ctx, const qf_linear_desc *desc, const void *X_host, const void *qweight,
+                         const void *scales, const void *qzeros_or_null, void *Y_host, void *workspace,
+                         size_t workspace_bytes, void *stream);
+
+/* Which kernel family `desc` resolves to (QF_PATH_GEMV / QF_PATH_GEMM) and the K split it will use. */
+int qf_w4a16_plan(const qf_linear_desc *desc, int32_t *path_out, int32_t *split_k_out);
+
+/* Number of kernel launches this library has enqueued since it was loaded (all contexts). */
+int64_t qf_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QUANTFORGE_RT_H */

@@ -1,0 +1,260 @@
+// C ABI of the runtime (include/quantforge_rt.h): argument checks, planning, dispatch.
+#include <cstring>
+#include <new>
+
+#include "qf_common.cuh"
+
+namespace qf {
+
+std::atomic<long long> g_launch_count{0};
+
+static constexpr int kSmCount = 148;  // planning constant: the library targets B200 only
+
+static bool aligned16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
+
+int make_plan(const qf_linear_desc *d, Plan *p, std::string *why) {
+    auto bad = [&](int st, const char *m) {
+        if (why) *why = m;
+        return st;
+    };
+    if (!d) return bad(QF_ERR_BAD_ARG, "desc is null");
+    if (d->M < 0 || d->N <= 0 || d->K <= 0) return bad(QF_ERR_BAD_ARG, "M, N, K must be positive (M may be 0)");
+    if (d->K % 128 != 0) return bad(QF_ERR_BAD_ARG, "K must be a multiple of 128");
+    if (d->N % 16 != 0) return bad(QF_ERR_BAD_ARG, "N must be a multiple of 16");
+    if (d->group_size <= 0 || d->group_size % 128 != 0 || d->K % d->group_size != 0)
+        return bad(QF_ERR_UNSUPPORTED, "group_size must be a multiple of 128 that divides K");
+    if (d->act_dtype != QF_F16 && d->act_dtype != QF_BF16)
+        return bad(QF_ERR_UNSUPPORTED, "act_dtype must be QF_F16 or QF_BF16");
+    if (d->out_dtype != QF_F16 && d->out_dtype != QF_BF16 && d->out_dtype != QF_F32)
+        return bad(QF_ERR_UNSUPPORTED, "out_dtype must be QF_F16, QF_BF16 or QF_F32");
+    if (d->zero_mode != QF_ZERO_CONST && d->zero_mode != QF_ZERO_U4 && d->zero_mode != QF_ZERO_I8)
+        return bad(QF_ERR_BAD_ARG, "unknown zero_mode");
+    if (d->zero_mode == QF_ZERO_CONST && (d->zero_const < -128 || d->zero_const > 127))
+        return bad(QF_ERR_BAD_ARG, "zero_const must fit a signed 8-bit zero point");
+    if (d->split_k < 0) return bad(QF_ERR_BAD_ARG, "split_k must be >= 0");
+    for (int i = 0; i < 5; ++i)
+        if (d->reserved[i] != 0) return bad(QF_ERR_BAD_ARG, "reserved fields must be zero");
+
+    int path = d->path;
+    if (path == QF_PATH_AUTO) path = QF_PATH_GEMV;  // TEMP until the tcgen05 path lands
+    if (path != QF_PATH_GEMV && path != QF_PATH_GEMM) return bad(QF_ERR_BAD_ARG, "unknown path");
+    if (path == QF_PATH_GEMM && d->N % 128 != 0) {
+        if (d->path == QF_PATH_GEMM) return bad(QF_ERR_BAD_ARG, "the GEMM path needs N to be a multiple of 128");
+        path = QF_PATH_GEMV;
+    }
+    p->path = path;
+    const int chunks = (int)(d->K / 128);
+    if (path == QF_PATH_GEMV) {
+        p->m_tiles = (int)((d->M + 7) / 8);
+        if (p->m_tiles < 1) p->m_tiles = 1;
+        p->bn = 8;
+        const int64_t col_blocks = (d->N + 63) / 64;
+        int split;
+        if (d->split_k > 0) {
+            split = d->split_k;
+        } else {
+            const int64_t base = col_blocks * p->m_tiles;
+            const int64_t target = (int64_t)kSmCount * 4;
+            split = (int)((target + base / 2) / base);
+            const int max_split = chunks / 4 > 0 ? chunks / 4 : 1;
+            if (split > max_split) split = max_split;
+            if (split < 1) split = 1;
+        }
+        if (split > chunks) split = chunks;
+        int cps = (chunks + split - 1) / split;
+        if (cps > 48) cps = 48;
+        split = (chunks + cps - 1) / cps;
+        p->split_k = split;
+        p->chunks_per_split = cps;
+        if (split > 1) {
+            p->ws_partial_bytes = (size_t)split * p->m_tiles * 8 * d->N * sizeof(float);
+            p->ws_counter_bytes = (((size_t)col_blocks * p->m_tiles * sizeof(int)) + 255) & ~(size_t)255;
+        } else {
+            p->ws_partial_bytes = 0;
+            p->ws_counter_bytes = 0;
+        }
+    } else {
+        return bad(QF_ERR_UNIMPLEMENTED, "GEMM path not built");
+    }
+    return QF_OK;
+}
+
+static int check_linear_args(qf_ctx *ctx, const qf_linear_desc *d, const void *X, const void *qw, const void *scales,
+                             const void *zeros, const void *Y) {
+    if (!ctx) return QF_ERR_BAD_ARG;
+    if (!X || !qw || !scales || !Y) return fail(ctx, QF_ERR_BAD_ARG, "null tensor pointer");
+    if (d->zero_mode != QF_ZERO_CONST && !zeros) return fail(ctx, QF_ERR_BAD_ARG, "zero_mode needs a qzeros tensor");
+    if (d->zero_mode == QF_ZERO_U4 && d->N % 8 != 0) return fail(ctx, QF_ERR_BAD_ARG, "QF_ZERO_U4 needs N % 8 == 0");
+    if (!aligned16(X) || !aligned16(qw) || !aligned16(scales) || !aligned16(Y) || (zeros && !aligned16(zeros)))
+        return fail(ctx, QF_ERR_BAD_ARG, "device pointers must be 16-byte aligned");
+    return QF_OK;
+}
+
+}  // namespace qf
+
+using namespace qf;
+
+extern "C" {
+
+int qf_version(void) { return QF_RT_VERSION; }
+
+const char *qf_status_string(int status) {
+    switch (status) {
+        case QF_OK: return "QF_OK";
+        case QF_ERR_BAD_ARG: return "QF_ERR_BAD_ARG";
+        case QF_ERR_UNSUPPORTED: return "QF_ERR_UNSUPPORTED";
+        case QF_ERR_CUDA: return "QF_ERR_CUDA";
+        case QF_ERR_NCCL: return "QF_ERR_NCCL";
+        case QF_ERR_TIMEOUT: return "QF_ERR_TIMEOUT";
+        case QF_ERR_UNIMPLEMENTED: return "QF_ERR_UNIMPLEMENTED";
+        case QF_ERR_WORKSPACE: return "QF_ERR_WORKSPACE";
+        default: return "QF_ERR_UNKNOWN";
+    }
+}
+
+int qf_ctx_create(qf_ctx **out, int device) {
+    if (!out) return QF_ERR_BAD_ARG;
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) return QF_ERR_CUDA;  // no CPU fallback exists
+    if (device < 0 || device >= count) return QF_ERR_BAD_ARG;
+    if (cudaSetDevice(device) != cudaSuccess) return QF_ERR_CUDA;
+    qf_ctx *ctx = new (std::nothrow) qf_ctx();
+    if (!ctx) return QF_ERR_CUDA;
+    ctx->device = device;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+        delete ctx;
+        return QF_ERR_CUDA;
+    }
+    ctx->sm_count = prop.multiProcessorCount;
+    if (prop.major != 10) {
+        delete ctx;
+        return QF_ERR_UNSUPPORTED;  // built for sm_100a only
+    }
+    int st = gemv_init(ctx);
+    if (st == QF_OK) st = gemm_init(ctx);
+    if (st != QF_OK) {
+        delete ctx;
+        return st;
+    }
+    *out = ctx;
+    return QF_OK;
+}
+
+int qf_ctx_destroy(qf_ctx *ctx) {
+    if (!ctx) return QF_OK;
+    cudaSetDevice(ctx->device);
+    if (ctx->stage_x) cudaFree(ctx->stage_x);
+    if (ctx->stage_y) cudaFree(ctx->stage_y);
+    if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->host_status) cudaFreeHost(ctx->host_status);
+    delete ctx;
+    return QF_OK;
+}
+
+const char *qf_last_error(const qf_ctx *ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+
+int qf_unpack_int4(qf_ctx *ctx, const void *packed_i8, void *out_i8, int64_t rows, int64_t packed_cols, void *stream) {
+    if (!ctx) return QF_ERR_BAD_ARG;
+    if (rows < 0 || packed_cols < 0) return fail(ctx, QF_ERR_BAD_ARG, "negative extent");
+    if (rows == 0 || packed_cols == 0) return QF_OK;
+    if (!packed_i8 || !out_i8) return fail(ctx, QF_ERR_BAD_ARG, "null tensor pointer");
+    if (((uintptr_t)out_i8 & 1u) != 0) return fail(ctx, QF_ERR_BAD_ARG, "output must be 2-byte aligned");
+    return launch_unpack(ctx, packed_i8, out_i8, rows, packed_cols, (cudaStream_t)stream);
+}
+
+int qf_dequant_w4(qf_ctx *ctx, const qf_linear_desc *desc, const void *qweight, const void *scales,
+                  const void *qzeros_or_null, void *w_out, void *stream) {
+    if (!ctx) return QF_ERR_BAD_ARG;
+    if (!desc) return fail(ctx, QF_ERR_BAD_ARG, "desc is null");
+    qf_linear_desc d = *desc;
+    d.M = 1;
+    d.path = QF_PATH_GEMV;
+    d.out_dtype = d.act_dtype;
+    Plan plan;
+    std::string why;
+    int st = make_plan(&d, &plan, &why);
+    if (st != QF_OK) return fail(ctx, st, why);
+    st = check_linear_args(ctx, &d, w_out, qweight, scales, qzeros_or_null, w_out);
+    if (st != QF_OK) return st;
+    return launch_dequant(ctx, &d, qweight, scales, qzeros_or_null, w_out, (cudaStream_t)stream);
+}
+
+size_t qf_w4a16_workspace_bytes(const qf_linear_desc *desc) {
+    Plan plan;
+    if (make_plan(desc, &plan, nullptr) != QF_OK) return 0;
+    return plan.ws_partial_bytes + plan.ws_counter_bytes;
+}
+
+int qf_w4a16_plan(const qf_linear_desc *desc, int32_t *path_out, int32_t *split_k_out) {
+    Plan plan;
+    int st = make_plan(desc, &plan, nullptr);
+    if (st != QF_OK) return st;
+    if (path_out) *path_out = plan.path;
+    if (split_k_out) *split_k_out = plan.split_k;
+    return QF_OK;
+}
+
+int qf_w4a16_linear(qf_ctx *ctx, const qf_linear_desc *desc, const void *X, const void *qweight, const void *scales,
+                    const void *qzeros_or_null, void *Y, void *workspace, size_t workspace_bytes, void *stream) {
+    if (!ctx) return QF_ERR_BAD_ARG;
+    Plan plan;
+    std::string why;
+    int st = make_plan(desc, &plan, &why);
+    if (st != QF_OK) return fail(ctx, st, why);
+    if (desc->M == 0) return QF_OK;
+    st = check_linear_args(ctx, desc, X, qweight, scales, qzeros_or_null, Y);
+    if (st != QF_OK) return st;
+    const size_t need = plan.ws_partial_bytes + plan.ws_counter_bytes;
+    if (need > 0) {
+        if (!workspace || workspace_bytes < need)
+            return fail(ctx, QF_ERR_WORKSPACE, "workspace smaller than qf_w4a16_workspace_bytes(desc)");
+        if (!aligned16(workspace)) return fail(ctx, QF_ERR_BAD_ARG, "workspace must be 16-byte aligned");
+    }
+    if (plan.path == QF_PATH_GEMV)
+        return launch_gemv(ctx, desc, plan, X, qweight, scales, qzeros_or_null, Y, workspace, (cudaStream_t)stream);
+    return launch_gemm(ctx, desc, plan, X, qweight, scales, qzeros_or_null, Y, workspace, (cudaStream_t)stream);
+}
+
+static int grow(qf_ctx *ctx, void **buf, size_t *have, size_t need) {
+    if (*have >= need) return QF_OK;
+    if (*buf) {
+        QF_CUDA_TRY(ctx, cudaFree(*buf));
+        *buf = nullptr;
+        *have = 0;
+    }
+    size_t cap = (need + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
+    QF_CUDA_TRY(ctx, cudaMalloc(buf, cap));
+    *have = cap;
+    return QF_OK;
+}
+
+int qf_w4a16_linear_host(qf_ctx *ctx, const qf_linear_desc *desc, const void *X_host, const void *qweight,
+                         const void *scales, const void *qzeros_or_null, void *Y_host, void *workspace,
+                         size_t workspace_bytes, void *stream) {
+    if (!ctx) return QF_ERR_BAD_ARG;
+    if (!desc) return fail(ctx, QF_ERR_BAD_ARG, "desc is null");
+    if (!X_host || !Y_host) return fail(ctx, QF_ERR_BAD_ARG, "null host pointer");
+    if (desc->M == 0) return QF_OK;
+    if (desc->M < 0 || desc->N <= 0 || desc->K <= 0) return fail(ctx, QF_ERR_BAD_ARG, "bad shape");
+    const size_t xb = (size_t)desc->M * desc->K * 2;
+    const size_t yb = (size_t)desc->M * desc->N * (desc->out_dtype == QF_F32 ? 4 : 2);
+    int st = grow(ctx, &ctx->stage_x, &ctx->stage_x_bytes, xb);
+    if (st != QF_OK) return st;
+    st = grow(ctx, &ctx->stage_y, &ctx->stage_y_bytes, yb);
+    if (st != QF_OK) return st;
+    cudaStream_t s = (cudaStream_t)stream;
+    QF_CUDA_TRY(ctx, cudaMemcpyAsync(ctx->stage_x, X_host, xb, cudaMemcpyHostToDevice, s));
+    st = qf_w4a16_linear(ctx, desc, ctx->stage_x, qweight, scales, qzeros_or_null, ctx->stage_y, workspace,
+                         workspace_bytes, stream);
+    if (st != QF_OK) return st;
+    QF_CUDA_TRY(ctx, cudaMemcpyAsync(Y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, s));
+    QF_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+    return QF_OK;
+}
+
+int64_t qf_launch_count(void) { return (int64_t)g_launch_count.load(); }
+
+}  // extern "C"

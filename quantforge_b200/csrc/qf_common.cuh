@@ -1,0 +1,198 @@
+// Shared device helpers and host-side context for the QuantForge B200 runtime.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <string>
+
+#include "quantforge_rt.h"
+
+namespace qf {
+
+// ---------------------------------------------------------------------------------------------
+// Host context
+// ---------------------------------------------------------------------------------------------
+struct TensorMapCacheEntry;
+
+}  // namespace qf
+
+struct qf_ctx {
+    int device = 0;
+    int sm_count = 148;
+    std::string last_error;
+    // staging for the *_host entry points (grown on demand, freed with the context)
+    void *stage_x = nullptr;
+    size_t stage_x_bytes = 0;
+    void *stage_y = nullptr;
+    size_t stage_y_bytes = 0;
+    // device status word written by kernels whose bounded waits expire (tcgen05 path)
+    int *dev_status = nullptr;
+    int *host_status = nullptr;  // pinned mirror
+};
+
+namespace qf {
+
+extern std::atomic<long long> g_launch_count;
+
+inline int fail(qf_ctx *ctx, int status, const std::string &msg) {
+    if (ctx) ctx->last_error = msg;
+    return status;
+}
+
+inline int cuda_fail(qf_ctx *ctx, cudaError_t e, const char *what) {
+    return fail(ctx, QF_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+#define QF_CUDA_TRY(ctx, expr)                                   \
+    do {                                                         \
+        cudaError_t _e = (expr);                                 \
+        if (_e != cudaSuccess) return cuda_fail(ctx, _e, #expr); \
+    } while (0)
+
+struct Plan {
+    int path;            // QF_PATH_GEMV / QF_PATH_GEMM
+    int split_k;         // number of K splits
+    int chunks_per_split;  // GEMV: 128-code chunks per split; GEMM: k-blocks per split
+    int m_tiles;         // GEMV: ceil(M/8); GEMM: batch tiles
+    int bn;              // GEMM: batch tile width (MMA N)
+    size_t ws_partial_bytes;
+    size_t ws_counter_bytes;
+};
+
+// Validates `d` and fills the launch plan. Returns QF_OK or an error status; `why` receives a message.
+int make_plan(const qf_linear_desc *d, Plan *p, std::string *why);
+
+// kernels (defined in their own translation units)
+int launch_unpack(qf_ctx *ctx, const void *packed, void *out, int64_t rows, int64_t packed_cols, cudaStream_t s);
+int launch_dequant(qf_ctx *ctx, const qf_linear_desc *d, const void *qw, const void *scales, const void *zeros,
+                   void *w_out, cudaStream_t s);
+int launch_gemv(qf_ctx *ctx, const qf_linear_desc *d, const Plan &p, const void *X, const void *qw,
+                const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s);
+int launch_gemm(qf_ctx *ctx, const qf_linear_desc *d, const Plan &p, const void *X, const void *qw,
+                const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s);
+int gemv_init(qf_ctx *ctx);
+int gemm_init(qf_ctx *ctx);
+
+// ---------------------------------------------------------------------------------------------
+// Device helpers: nibble -> f16 / bf16 conversion with zero and scale applied in registers.
+// ---------------------------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & b) | c
+    return r;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ uint32_t sub_f16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t mul_f16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t fma_f16x2(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+// 16-bit float bit patterns of small integers (exact in both formats for |v| <= 256).
+__device__ __forceinline__ uint32_t int_to_f16_bits(int v) {
+    return (uint32_t)__half_as_ushort(__int2half_rn(v));
+}
+__device__ __forceinline__ uint32_t int_to_bf16_bits(int v) {
+    return __float_as_uint((float)v) >> 16;  // |v| <= 256 has <= 8 significant bits: exact
+}
+__device__ __forceinline__ uint32_t dup16(uint32_t h) { return h | (h << 16); }
+
+// Per (row, group) constants for the converters below.
+//   f16 : zsub = (1024 + z) x2, zfma = -(64 + z) x2      bf16: zsub = (128 + z) x2, zfma unused
+template <bool BF16>
+struct ZeroScale {
+    uint32_t zsub, zfma, s2;
+    __device__ __forceinline__ void set(int z, uint32_t scale_bits) {
+        s2 = dup16(scale_bits & 0xffffu);
+        if (BF16) {
+            zsub = dup16(int_to_bf16_bits(128 + z));
+            zfma = 0;
+        } else {
+            zsub = dup16(int_to_f16_bits(1024 + z));
+            zfma = dup16(int_to_f16_bits(-(64 + z)));
+        }
+    }
+};
+
+// One packed word w holds codes c0..c7 (c_i = (w >> 4i) & 0xF).  Produces, in the activation type,
+//   p[i] = ( (c_i - z) * s , (c_{i+4} - z) * s )   (low half, high half),  i = 0..3
+// with the same roundings as `f16(sitofp(q)) - f16(sitofp(z))` (exact) followed by one
+// round-to-nearest-even multiply (the reference's qf.dequant arithmetic).
+//   f16 : (w & 0x000f000f) | 0x6400.. is 1024 + c  ;  (w & 0x00f000f0) | 0x6400.. is 1024 + 16c,
+//         brought back by fma(v, 1/16, -(64 + z)) = c - z, exact.
+//   bf16: ((w >> 4i) & 0x000f000f) | 0x4300.. is 128 + c.
+template <bool BF16>
+__device__ __forceinline__ void dequant8(uint32_t w, const ZeroScale<BF16> &zs, uint32_t (&p)[4]) {
+    if (BF16) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t v = lop3_and_or(w >> (4 * i), 0x000f000fu, 0x43004300u);
+            p[i] = mul_bf16x2(sub_bf16x2(v, zs.zsub), zs.s2);
+        }
+    } else {
+        const uint32_t w8 = w >> 8;
+        uint32_t v0 = lop3_and_or(w, 0x000f000fu, 0x64006400u);
+        uint32_t v1 = lop3_and_or(w, 0x00f000f0u, 0x64006400u);
+        uint32_t v2 = lop3_and_or(w8, 0x000f000fu, 0x64006400u);
+        uint32_t v3 = lop3_and_or(w8, 0x00f000f0u, 0x64006400u);
+        p[0] = mul_f16x2(sub_f16x2(v0, zs.zsub), zs.s2);
+        p[1] = mul_f16x2(fma_f16x2(v1, 0x2c002c00u, zs.zfma), zs.s2);
+        p[2] = mul_f16x2(sub_f16x2(v2, zs.zsub), zs.s2);
+        p[3] = mul_f16x2(fma_f16x2(v3, 0x2c002c00u, zs.zfma), zs.s2);
+    }
+}
+
+// Zero point of (group gi, column n) for the three storage modes.
+template <int ZMODE>
+__device__ __forceinline__ int load_zero(const void *zeros, int zero_const, int64_t gi, int64_t n, int64_t N) {
+    if (ZMODE == QF_ZERO_CONST) return zero_const;
+    if (ZMODE == QF_ZERO_U4) {
+        const uint32_t *z = reinterpret_cast<const uint32_t *>(zeros);
+        return (int)((__ldg(z + gi * (N >> 3) + (n >> 3)) >> (4 * (int)(n & 7))) & 0xFu);
+    }
+    return (int)__ldg(reinterpret_cast<const int8_t *>(zeros) + gi * N + n);
+}
+
+__device__ __forceinline__ void store_out(void *Y, int out_dtype, int64_t idx, float v) {
+    if (out_dtype == QF_F32) {
+        reinterpret_cast<float *>(Y)[idx] = v;
+    } else if (out_dtype == QF_F16) {
+        reinterpret_cast<__half *>(Y)[idx] = __float2half_rn(v);
+    } else {
+        reinterpret_cast<__nv_bfloat16 *>(Y)[idx] = __float2bfloat16_rn(v);
+    }
+}
+
+#endif  // __CUDACC__
+
+}  // namespace qf

@@ -1,0 +1,271 @@
+"""Operators of the W4A16 path on torch CUDA tensors.
+
+The names and argument meaning of `pack_int4`, `unpack_int4` and `gemv_int4` follow the
+reference's python/quantforge/baseline.py (:17-31, :34-49, :52-72).  Every compute call goes
+through the C ABI into hand-written sm_100a kernels; tensors on the CPU are rejected (there is
+no CPU implementation in this package).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import (QF_BF16, QF_F16, QF_F32, QF_PATH_AUTO, QF_ZERO_CONST, QF_ZERO_I8, QF_ZERO_U4, LinearDesc,
+                   QuantForgeError)
+
+_DT = {torch.float16: QF_F16, torch.bfloat16: QF_BF16, torch.float32: QF_F32}
+_ctxs: dict[int, ctypes.c_void_p] = {}
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _ctx(device: torch.device) -> ctypes.c_void_p:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _ctxs:
+        lib = _lib.load()
+        h = ctypes.c_void_p()
+        st = lib.qf_ctx_create(ctypes.byref(h), idx)
+        if st != 0:
+            raise QuantForgeError(st, _lib.status_name(st), f"qf_ctx_create(device={idx}) failed")
+        _ctxs[idx] = h
+    return _ctxs[idx]
+
+
+def _check(st: int, ctx) -> None:
+    if st != 0:
+        raise QuantForgeError(st, _lib.status_name(st), _lib.load().qf_last_error(ctx).decode())
+
+
+def _need_cuda(*tensors: Optional[torch.Tensor]) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise ValueError("quantforge_b200 runs on CUDA tensors only (no CPU fallback)")
+        if dev is not None and t.device != dev:
+            raise ValueError("all tensors must live on the same device")
+        dev = t.device
+    return dev
+
+
+def _stream(device: torch.device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+
+
+def launch_count() -> int:
+    """Kernel launches enqueued by the runtime library since it was loaded."""
+    return int(_lib.load().qf_launch_count())
+
+
+# --------------------------------------------------------------------------------------------
+# packing helpers (layout only; any device)
+# --------------------------------------------------------------------------------------------
+def pack_int4(weights: torch.Tensor) -> torch.Tensor:
+    """int8[..., 2n] codes in [0, 15] -> int8[..., n]; even index -> low nibble."""
+    if weights.dtype != torch.int8:
+        raise TypeError("pack_int4 expects an int8 tensor of codes")
+    if weights.shape[-1] % 2 != 0:
+        raise ValueError("last dim must be even")
+    low = weights[..., 0::2] & 0x0F
+    high = weights[..., 1::2] & 0x0F
+    return (low | (high << 4)).to(torch.int8)
+
+
+def pack_zeros_u4(zeros: torch.Tensor) -> torch.Tensor:
+    """zero codes [G, N] in [0, 15] -> int32[G, N/8] holding 8 codes per word along N, LSB first."""
+    G, N = zeros.shape
+    if N % 8 != 0:
+        raise ValueError("N must be a multiple of 8")
+    z = zeros.to(torch.int64).reshape(G, N // 8, 8) & 0xF
+    shifts = torch.arange(8, device=zeros.device, dtype=torch.int64) * 4
+    words = (z << shifts).sum(dim=-1)
+    words = torch.where(words >= 2 ** 31, words - 2 ** 32, words)
+    return words.to(torch.int32).contiguous()
+
+
+# --------------------------------------------------------------------------------------------
+# qf.unpack
+# --------------------------------------------------------------------------------------------
+def unpack_int4(packed: torch.Tensor) -> torch.Tensor:
+    """int8[..., n] -> int8[..., 2n]: out[2i] = b & 0xF, out[2i+1] = (b >> 4) & 0xF (logical shift)."""
+    dev = _need_cuda(packed)
+    if packed.dtype not in (torch.int8, torch.uint8):
+        raise TypeError("unpack_int4 expects int8 (or uint8) packed bytes")
+    packed = packed.contiguous()
+    out = torch.empty(packed.shape[:-1] + (packed.shape[-1] * 2,), dtype=torch.int8, device=dev)
+    rows = packed.numel() // packed.shape[-1] if packed.shape[-1] else 0
+    ctx = _ctx(dev)
+    with torch.cuda.device(dev):
+        _check(_lib.load().qf_unpack_int4(ctx, _ptr(packed), _ptr(out), rows, packed.shape[-1], _stream(dev)), ctx)
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# linear
+# --------------------------------------------------------------------------------------------
+def _make_desc(M, N, K, group_size, act_dtype, out_dtype, zeros, zero_const, path, split_k) -> LinearDesc:
+    d = LinearDesc()
+    d.M, d.N, d.K = M, N, K
+    d.group_size = group_size
+    d.act_dtype = _DT[act_dtype]
+    d.out_dtype = _DT[out_dtype]
+    if zeros is None:
+        d.zero_mode, d.zero_const = QF_ZERO_CONST, int(zero_const)
+    elif zeros.dtype == torch.int8:
+        d.zero_mode = QF_ZERO_I8
+    elif zeros.dtype == torch.int32:
+        d.zero_mode = QF_ZERO_U4
+    else:
+        raise TypeError("zeros must be None (constant), int8 [G,N] or packed int32 [G,N/8]")
+    d.path = path
+    d.split_k = split_k
+    return d
+
+
+def workspace_bytes(desc: LinearDesc) -> int:
+    return int(_lib.load().qf_w4a16_workspace_bytes(ctypes.byref(desc)))
+
+
+def _workspace(dev: torch.device, nbytes: int) -> Optional[torch.Tensor]:
+    """Per (device, stream) zero-initialised scratch, grown on demand. Calls on one stream are ordered."""
+    if nbytes == 0:
+        return None
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(dev).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
+        _workspaces[key] = ws
+    return ws
+
+
+def _check_linear_tensors(x, qweight, scales, zeros, group_size):
+    if x.dim() != 2 or qweight.dim() != 2:
+        raise ValueError("x must be [M, K] and qweight [N, K/2] (int8) or [N, K/8] (int32)")
+    M, K = x.shape
+    if qweight.dtype in (torch.int8, torch.uint8):
+        N, kw = qweight.shape[0], qweight.shape[1] * 2
+    elif qweight.dtype == torch.int32:
+        N, kw = qweight.shape[0], qweight.shape[1] * 8
+    else:
+        raise TypeError("qweight must be int8/uint8 [N, K/2] or int32 [N, K/8]")
+    if kw != K:
+        raise ValueError(f"qweight holds {kw} codes per row but x has K={K}")
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("x must be float16 or bfloat16")
+    if scales.dtype != x.dtype:
+        raise TypeError("scales must have the dtype of x")
+    G = K // group_size if group_size > 0 and K % group_size == 0 else -1
+    if tuple(scales.shape) != (G, N):
+        raise ValueError(f"scales must be [K/group_size, N] = [{G}, {N}], got {tuple(scales.shape)}")
+    if zeros is not None:
+        want = (G, N) if zeros.dtype == torch.int8 else (G, N // 8)
+        if tuple(zeros.shape) != want:
+            raise ValueError(f"zeros must be {want}, got {tuple(zeros.shape)}")
+    return M, N, K
+
+
+def w4a16_linear(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor] = None,
+                 group_size: int = 128, zero_const: int = 8, out_dtype: Optional[torch.dtype] = None,
+                 path: int = QF_PATH_AUTO, split_k: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Y[M,N] = X[M,K] . dequant(unpack(qweight))^T, fp32 accumulation, W never materialised.
+
+    x        f16|bf16 [M, K]
+    qweight  int8 [N, K/2] (two codes per byte along K) or int32 [N, K/8]
+    scales   same dtype as x, [K/group_size, N]
+    zeros    None (constant `zero_const`), int8 [G, N] or packed int32 [G, N/8] (pack_zeros_u4)
+    """
+    dev = _need_cuda(x, qweight, scales, zeros)
+    M, N, K = _check_linear_tensors(x, qweight, scales, zeros, group_size)
+    out_dtype = out_dtype or x.dtype
+    x, qweight, scales = x.contiguous(), qweight.contiguous(), scales.contiguous()
+    zeros = zeros.contiguous() if zeros is not None else None
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=dev)
+    elif tuple(out.shape) != (M, N) or out.dtype != out_dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [M, N] tensor of out_dtype")
+    d = _make_desc(M, N, K, group_size, x.dtype, out_dtype, zeros, zero_const, path, split_k)
+    ctx = _ctx(dev)
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, workspace_bytes(d))
+        st = _lib.load().qf_w4a16_linear(ctx, ctypes.byref(d), _ptr(x), _ptr(qweight), _ptr(scales), _ptr(zeros),
+                                         _ptr(out), _ptr(ws), ws.numel() if ws is not None else 0, _stream(dev))
+    _check(st, ctx)
+    return out
+
+
+def w4a16_linear_host(x_host: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
+                      zeros: Optional[torch.Tensor] = None, group_size: int = 128, zero_const: int = 8,
+                      out_dtype: Optional[torch.dtype] = None, out_host: Optional[torch.Tensor] = None,
+                      path: int = QF_PATH_AUTO) -> torch.Tensor:
+    """Same linear with activations and result in HOST memory (pinned for speed); weights stay on the GPU."""
+    if x_host.is_cuda:
+        raise ValueError("x_host must be a CPU tensor")
+    dev = _need_cuda(qweight, scales, zeros)
+    M, N, K = _check_linear_tensors(x_host, qweight, scales, zeros, group_size)
+    out_dtype = out_dtype or x_host.dtype
+    x_host = x_host.contiguous()
+    if out_host is None:
+        out_host = torch.empty((M, N), dtype=out_dtype, pin_memory=True)
+    d = _make_desc(M, N, K, group_size, x_host.dtype, out_dtype, zeros, zero_const, path, 0)
+    ctx = _ctx(dev)
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, workspace_bytes(d))
+        st = _lib.load().qf_w4a16_linear_host(ctx, ctypes.byref(d), _ptr(x_host), _ptr(qweight), _ptr(scales),
+                                              _ptr(zeros), _ptr(out_host), _ptr(ws),
+                                              ws.numel() if ws is not None else 0, _stream(dev))
+    _check(st, ctx)
+    return out_host
+
+
+def dequant_w4(qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor] = None,
+               group_size: int = 128, zero_const: int = 8) -> torch.Tensor:
+    """qf.dequant(qf.unpack(qweight)) materialised: W[N, K] in the dtype of `scales`."""
+    dev = _need_cuda(qweight, scales, zeros)
+    N = qweight.shape[0]
+    K = qweight.shape[1] * (8 if qweight.dtype == torch.int32 else 2)
+    out = torch.empty((N, K), dtype=scales.dtype, device=dev)
+    d = _make_desc(1, N, K, group_size, scales.dtype, scales.dtype, zeros, zero_const, QF_PATH_AUTO, 0)
+    ctx = _ctx(dev)
+    qweight, scales = qweight.contiguous(), scales.contiguous()
+    zeros = zeros.contiguous() if zeros is not None else None
+    with torch.cuda.device(dev):
+        st = _lib.load().qf_dequant_w4(ctx, ctypes.byref(d), _ptr(qweight), _ptr(scales), _ptr(zeros), _ptr(out),
+                                       _stream(dev))
+    _check(st, ctx)
+    return out
+
+
+def gemv_int4(x: torch.Tensor, w_packed: torch.Tensor, scale: torch.Tensor, zero_point: torch.Tensor) -> torch.Tensor:
+    """Drop-in for the reference's `gemv_int4_baseline(x, w_packed, scale, zero_point)`.
+
+    x (M, K) f16, w_packed (N, K/2) int8, per-output-channel scale (N,) f16 and zero_point (N,) int8.
+    Per-channel quantisation is the group_size == K case of the group-wise kernel.
+    """
+    K = x.shape[1]
+    return w4a16_linear(x, w_packed, scale.reshape(1, -1).to(x.dtype), zero_point.reshape(1, -1).to(torch.int8),
+                        group_size=K, out_dtype=x.dtype)
+
+
+class W4A16Linear:
+    """A quantised linear layer whose weights live on one GPU: y = x . W^T."""
+
+    def __init__(self, qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor] = None,
+                 group_size: int = 128, zero_const: int = 8):
+        _need_cuda(qweight, scales, zeros)
+        self.qweight, self.scales, self.zeros = qweight.contiguous(), scales.contiguous(), zeros
+        self.group_size, self.zero_const = group_size, zero_const
+        self.N = qweight.shape[0]
+        self.K = qweight.shape[1] * (8 if qweight.dtype == torch.int32 else 2)
+
+    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return w4a16_linear(x, self.qweight, self.scales, self.zeros, self.group_size, self.zero_const, out_dtype,
+                            out=out)
