@@ -51,6 +51,15 @@ typedef enum qf_zero_mode { QF_ZERO_CONST = 0, QF_ZERO_U4 = 1, QF_ZERO_I8 = 2 } 
 /* Which kernel family serves a linear.  AUTO: M <= 8 -> GEMV kernel, M >= 9 -> tcgen05 GEMM kernel. */
 typedef enum qf_path { QF_PATH_AUTO = 0, QF_PATH_GEMV = 1, QF_PATH_GEMM = 2 } qf_path;
 
+/*
+ * Order of the eight 4-bit codes inside each 32-bit word of qweight.
+ *   QF_LAYOUT_CANONICAL   : nibble i holds code 8j+i (what qf.unpack defines; lib/Transforms/LowerUnpackToNVVM.cpp:254-265)
+ *   QF_LAYOUT_INTERLEAVED : nibbles hold codes 8j + {0,2,4,6,1,3,5,7}; produced once by qf_prepack_w4. With it the
+ *                           lop3 converter yields (k, k+1) pairs directly and the GEMM kernel skips a byte permute.
+ * Rows, words per row and everything else are unchanged: the prepack is a pure permutation inside each word.
+ */
+typedef enum qf_weight_layout { QF_LAYOUT_CANONICAL = 0, QF_LAYOUT_INTERLEAVED = 1 } qf_weight_layout;
+
 typedef struct qf_ctx qf_ctx;
 
 typedef struct qf_linear_desc {
@@ -62,7 +71,8 @@ typedef struct qf_linear_desc {
     int32_t zero_const;  /* used when zero_mode == QF_ZERO_CONST (8 = symmetric int4, 0 = the zp==0 fast path) */
     int32_t path;        /* qf_path */
     int32_t split_k;     /* 0 = heuristic; >0 forces the number of K splits */
-    int32_t reserved[5]; /* must be zero */
+    int32_t weight_layout; /* qf_weight_layout of qweight */
+    int32_t reserved[4]; /* must be zero */
 } qf_linear_desc;
 
 int qf_version(void);
@@ -117,6 +127,23 @@ int qf_w4a16_linear(qf_ctx *ctx, const qf_linear_desc *desc, const void *X, cons
 int qf_w4a16_linear_host(qf_ctx *ctx, const qf_linear_desc *desc, const void *X_host, const void *qweight,
                          const void *scales, const void *qzeros_or_null, void *Y_host, void *workspace,
                          size_t workspace_bytes, void *stream);
+
+/*
+ * One-time weight prepack: canonical -> QF_LAYOUT_INTERLEAVED (or back with to_canonical != 0).
+ * n_words = N * K / 8 32-bit words; in and out may alias. The inverse of the permutation exists so that
+ * unpack(prepack^-1(prepack(w))) == unpack(w) can be checked bit for bit. No reference counterpart: the
+ * reference never fixes a device weight layout (its packing helper is python/quantforge/baseline.py:17-31).
+ */
+int qf_prepack_w4(qf_ctx *ctx, const void *qweight_in, void *qweight_out, int64_t n_words, int to_canonical,
+                  void *stream);
+
+/*
+ * Sticky device-side status of this context: QF_OK, or QF_ERR_TIMEOUT when a kernel's bounded wait expired
+ * (the kernel then returned without finishing its tile). Reading it does not synchronise; call it after the
+ * stream has been synchronised. qf_ctx_clear_status resets it.
+ */
+int qf_ctx_status(const qf_ctx *ctx);
+int qf_ctx_clear_status(qf_ctx *ctx);
 
 /* Which kernel family `desc` resolves to (QF_PATH_GEMV / QF_PATH_GEMM) and the K split it will use. */
 int qf_w4a16_plan(const qf_linear_desc *desc, int32_t *path_out, int32_t *split_k_out);

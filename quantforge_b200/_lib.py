@@ -15,12 +15,13 @@ QF_OK = 0
 QF_F16, QF_BF16, QF_F32 = 0, 1, 2
 QF_ZERO_CONST, QF_ZERO_U4, QF_ZERO_I8 = 0, 1, 2
 QF_PATH_AUTO, QF_PATH_GEMV, QF_PATH_GEMM = 0, 1, 2
+QF_LAYOUT_CANONICAL, QF_LAYOUT_INTERLEAVED = 0, 1
 
 # every symbol include/quantforge_rt.h declares
 EXPORTS = [
     "qf_version", "qf_status_string", "qf_ctx_create", "qf_ctx_destroy", "qf_last_error", "qf_unpack_int4",
     "qf_dequant_w4", "qf_w4a16_workspace_bytes", "qf_w4a16_linear", "qf_w4a16_linear_host", "qf_w4a16_plan",
-    "qf_launch_count",
+    "qf_launch_count", "qf_prepack_w4", "qf_ctx_status", "qf_ctx_clear_status",
 ]
 
 
@@ -29,7 +30,7 @@ class LinearDesc(ctypes.Structure):
         ("M", ctypes.c_int64), ("N", ctypes.c_int64), ("K", ctypes.c_int64),
         ("group_size", ctypes.c_int32), ("act_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
         ("zero_mode", ctypes.c_int32), ("zero_const", ctypes.c_int32), ("path", ctypes.c_int32),
-        ("split_k", ctypes.c_int32), ("reserved", ctypes.c_int32 * 5),
+        ("split_k", ctypes.c_int32), ("weight_layout", ctypes.c_int32), ("reserved", ctypes.c_int32 * 4),
     ]
 
 
@@ -70,6 +71,9 @@ def load() -> ctypes.CDLL:
     lib.qf_w4a16_linear_host.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp, sz, vp]
     lib.qf_w4a16_plan.argtypes = [dp, ctypes.POINTER(i32), ctypes.POINTER(i32)]
     lib.qf_launch_count.restype = i64
+    lib.qf_prepack_w4.argtypes = [vp, vp, vp, i64, ctypes.c_int, vp]
+    lib.qf_ctx_status.argtypes = [vp]
+    lib.qf_ctx_clear_status.argtypes = [vp]
     _lib = lib
     return lib
 

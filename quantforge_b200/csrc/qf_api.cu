@@ -9,6 +9,10 @@ namespace qf {
 std::atomic<long long> g_launch_count{0};
 
 static constexpr int kSmCount = 148;  // planning constant: the library targets B200 only
+// The split-K arrival counters occupy a FIXED region at the start of the workspace, so that a
+// workspace reused by linears of different shapes never exposes stale partial sums as counters.
+static constexpr int kMaxCounters = 16384;
+static constexpr size_t kCounterBytes = (size_t)kMaxCounters * sizeof(int);
 
 static bool aligned16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
 
@@ -32,15 +36,21 @@ int make_plan(const qf_linear_desc *d, Plan *p, std::string *why) {
     if (d->zero_mode == QF_ZERO_CONST && (d->zero_const < -128 || d->zero_const > 127))
         return bad(QF_ERR_BAD_ARG, "zero_const must fit a signed 8-bit zero point");
     if (d->split_k < 0) return bad(QF_ERR_BAD_ARG, "split_k must be >= 0");
-    for (int i = 0; i < 5; ++i)
+    if (d->weight_layout != QF_LAYOUT_CANONICAL && d->weight_layout != QF_LAYOUT_INTERLEAVED)
+        return bad(QF_ERR_BAD_ARG, "unknown weight_layout");
+    for (int i = 0; i < 4; ++i)
         if (d->reserved[i] != 0) return bad(QF_ERR_BAD_ARG, "reserved fields must be zero");
 
     int path = d->path;
-    if (path == QF_PATH_AUTO) path = QF_PATH_GEMV;  // TEMP until the tcgen05 path lands
+    if (path == QF_PATH_AUTO) path = (d->M <= 8) ? QF_PATH_GEMV : QF_PATH_GEMM;
     if (path != QF_PATH_GEMV && path != QF_PATH_GEMM) return bad(QF_ERR_BAD_ARG, "unknown path");
     if (path == QF_PATH_GEMM && d->N % 128 != 0) {
         if (d->path == QF_PATH_GEMM) return bad(QF_ERR_BAD_ARG, "the GEMM path needs N to be a multiple of 128");
         path = QF_PATH_GEMV;
+    }
+    if (path == QF_PATH_GEMV && d->weight_layout != QF_LAYOUT_CANONICAL) {
+        if (d->N % 128 != 0) return bad(QF_ERR_UNSUPPORTED, "interleaved weights need N to be a multiple of 128");
+        path = QF_PATH_GEMM;  // only the tcgen05 kernel reads the interleaved layout
     }
     p->path = path;
     const int chunks = (int)(d->K / 128);
@@ -66,15 +76,48 @@ int make_plan(const qf_linear_desc *d, Plan *p, std::string *why) {
         split = (chunks + cps - 1) / cps;
         p->split_k = split;
         p->chunks_per_split = cps;
+        if (col_blocks * p->m_tiles > kMaxCounters) split = 1, cps = chunks > 48 ? 48 : chunks;
+        if (cps * split < chunks) return bad(QF_ERR_UNSUPPORTED, "K too large for this N on the GEMV path");
+        p->split_k = split;
+        p->chunks_per_split = cps;
         if (split > 1) {
             p->ws_partial_bytes = (size_t)split * p->m_tiles * 8 * d->N * sizeof(float);
-            p->ws_counter_bytes = (((size_t)col_blocks * p->m_tiles * sizeof(int)) + 255) & ~(size_t)255;
+            p->ws_counter_bytes = kCounterBytes;
         } else {
             p->ws_partial_bytes = 0;
             p->ws_counter_bytes = 0;
         }
     } else {
-        return bad(QF_ERR_UNIMPLEMENTED, "GEMM path not built");
+        const int bn = d->M <= 16 ? 16 : d->M <= 32 ? 32 : d->M <= 64 ? 64 : d->M <= 128 ? 128 : 256;
+        const int bk = gemm_block_k(bn);
+        const int kblocks = (int)(d->K / bk);
+        p->bn = bn;
+        p->m_tiles = (int)((d->M + bn - 1) / bn);
+        if (p->m_tiles < 1) p->m_tiles = 1;
+        const int64_t tiles = (int64_t)p->m_tiles * (d->N / 128);
+        int split;
+        if (d->split_k > 0) {
+            split = d->split_k;
+        } else {
+            const int64_t slots = (int64_t)kSmCount * (bn <= 64 ? 2 : 1);
+            split = (int)(slots / tiles);
+            if (split < 1) split = 1;
+        }
+        if (split > kblocks) split = kblocks;
+        int kbps = (kblocks + split - 1) / split;
+        const int min_kbps = d->split_k > 0 ? 1 : (kblocks < 4 ? kblocks : 4);
+        if (kbps < min_kbps) kbps = min_kbps;
+        split = (kblocks + kbps - 1) / kbps;
+        if (tiles > kMaxCounters) split = 1, kbps = kblocks;
+        p->split_k = split;
+        p->chunks_per_split = kbps;
+        if (split > 1) {
+            p->ws_partial_bytes = (size_t)split * p->m_tiles * bn * d->N * sizeof(float);
+            p->ws_counter_bytes = kCounterBytes;
+        } else {
+            p->ws_partial_bytes = 0;
+            p->ws_counter_bytes = 0;
+        }
     }
     return QF_OK;
 }
@@ -148,7 +191,6 @@ int qf_ctx_destroy(qf_ctx *ctx) {
     cudaSetDevice(ctx->device);
     if (ctx->stage_x) cudaFree(ctx->stage_x);
     if (ctx->stage_y) cudaFree(ctx->stage_y);
-    if (ctx->dev_status) cudaFree(ctx->dev_status);
     if (ctx->host_status) cudaFreeHost(ctx->host_status);
     delete ctx;
     return QF_OK;
@@ -252,6 +294,28 @@ int qf_w4a16_linear_host(qf_ctx *ctx, const qf_linear_desc *desc, const void *X_
     if (st != QF_OK) return st;
     QF_CUDA_TRY(ctx, cudaMemcpyAsync(Y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, s));
     QF_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+    return QF_OK;
+}
+
+int qf_prepack_w4(qf_ctx *ctx, const void *qweight_in, void *qweight_out, int64_t n_words, int to_canonical,
+                  void *stream) {
+    if (!ctx) return QF_ERR_BAD_ARG;
+    if (n_words < 0) return fail(ctx, QF_ERR_BAD_ARG, "negative extent");
+    if (n_words == 0) return QF_OK;
+    if (!qweight_in || !qweight_out) return fail(ctx, QF_ERR_BAD_ARG, "null tensor pointer");
+    if (((uintptr_t)qweight_in & 3u) || ((uintptr_t)qweight_out & 3u))
+        return fail(ctx, QF_ERR_BAD_ARG, "weights must be 4-byte aligned");
+    return launch_prepack(ctx, qweight_in, qweight_out, n_words, to_canonical, (cudaStream_t)stream);
+}
+
+int qf_ctx_status(const qf_ctx *ctx) {
+    if (!ctx) return QF_ERR_BAD_ARG;
+    return ctx->host_status ? *(volatile int *)ctx->host_status : QF_OK;
+}
+
+int qf_ctx_clear_status(qf_ctx *ctx) {
+    if (!ctx) return QF_ERR_BAD_ARG;
+    if (ctx->host_status) *(volatile int *)ctx->host_status = QF_OK;
     return QF_OK;
 }
 

@@ -1,8 +1,593 @@
+// K3: W4A16 GEMM on the 5th-generation tensor cores (tcgen05), weights dequantised in the mainloop.
+//
+// Computes Y^T = W . X^T tile by tile so that the DEQUANTISED WEIGHTS are the MMA's A operand and
+// live only in tensor memory (TMEM):
+//   MMA M = 128 output features (weight rows, one per TMEM lane)
+//   MMA N = BN  rows of X (the batch), 16..256
+//   MMA K = 16  per instruction, BK codes per pipeline stage
+//
+// Roles inside a CTA (320 threads):
+//   warps 0-3, 4-7 : two converter groups, alternating k-blocks. Thread t of a group owns weight row
+//                    n0 + t: it reads the row's packed codes from the TMA-staged shared-memory tile,
+//                    converts them with lop3 / packed 16-bit arithmetic (zero and scale of its own
+//                    row and group held in registers), and writes the 16-bit operand straight into
+//                    TMEM lane t with tcgen05.st.  The same threads run the epilogue
+//                    (tcgen05.ld -> convert -> global store, or split-K partials).
+//   warp 8         : TMA producer (one elected thread): packed-weight tile and X tile per stage.
+//   warp 9         : TMEM allocation and, one elected thread, tcgen05.mma issue: A from TMEM,
+//                    B (= X tile, K-major, 128-byte swizzle) from shared memory, fp32 accumulate in TMEM.
+// Every mbarrier wait is bounded: on expiry the CTA raises an abort flag, records QF_ERR_TIMEOUT in
+// the context's status word, drains its own TMA copies, frees its TMEM and returns.
+// No multicast, no cluster launch: every CTA loads its own tiles.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
 #include "qf_common.cuh"
+
 namespace qf {
-int gemm_init(qf_ctx *) { return QF_OK; }
-int launch_gemm(qf_ctx *ctx, const qf_linear_desc *, const Plan &, const void *, const void *, const void *,
-                const void *, void *, void *, cudaStream_t) {
-    return fail(ctx, QF_ERR_UNIMPLEMENTED, "GEMM path not built");
+
+// ---------------------------------------------------------------------------------------------
+// configuration per batch-tile width
+// ---------------------------------------------------------------------------------------------
+template <int BN>
+struct GemmCfg {
+    static constexpr int BK = (BN <= 128) ? 128 : 64;           // codes per k-block
+    static constexpr int W_ROW_BYTES = BK / 2;                   // 64 or 32
+    static constexpr int W_STAGE_BYTES = 128 * W_ROW_BYTES;      // 8 KB or 4 KB
+    static constexpr int X_BOX_BYTES = BN * 128;                 // one 64-element box
+    static constexpr int X_STAGE_BYTES = X_BOX_BYTES * (BK / 64);
+    static constexpr int STAGE_BYTES = W_STAGE_BYTES + X_STAGE_BYTES;
+    static constexpr int STAGES = BN == 16 ? 8 : BN == 32 ? 6 : BN == 64 ? 4 : 5;
+    static constexpr int NA = BN <= 64 ? 3 : 4;                  // A operand buffers in TMEM
+    static constexpr int A_COLS = BK / 2;                        // 32-bit TMEM columns per A buffer
+    static constexpr int TMEM_COLS = (BN + NA * A_COLS) <= 256 ? 256 : 512;
+    static constexpr int CTAS_PER_SM = BN <= 64 ? 2 : 1;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+constexpr int GEMM_THREADS = 320;
+constexpr int GEMM_CONV_THREADS = 256;
+
+struct GemmParams {
+    const uint16_t *scales;
+    const void *zeros;
+    void *Y;
+    float *partial;
+    int *counters;
+    int *status;  // host-mapped status word
+    int64_t M, N, K;
+    int group_size;
+    int zero_mode, zero_const;
+    int out_dtype;
+    int kblocks;           // K / BK
+    int kblocks_per_split;
+    int split_k;
+    int interleaved;       // weight nibble order inside a word: 0 canonical, 1 pair-interleaved
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+
+// Bounded wait (about half a second of SM clocks). Returns false on expiry or when another role aborted.
+constexpr long long kWaitCycles = 1000000000LL;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    int it = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++it & 63) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitCycles) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+
+// D[tmem] (+)= A[tmem] . B[smem desc]
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on the mbarrier once all MMAs issued so far by this thread have completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// K-major shared-memory operand descriptor, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);        // start address
+    d |= (uint64_t)1 << 16;                            // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
+    d |= (uint64_t)1 << 46;                            // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ int load_zero_rt(const void *zeros, int zmode, int zconst, int64_t gi, int64_t n,
+                                            int64_t N) {
+    if (zmode == QF_ZERO_CONST) return zconst;
+    if (zmode == QF_ZERO_U4) return load_zero<QF_ZERO_U4>(zeros, zconst, gi, n, N);
+    return load_zero<QF_ZERO_I8>(zeros, zconst, gi, n, N);
+}
+
+// 4 packed words (32 codes along K) -> 16 registers of 16-bit pairs in natural k order.
+template <bool BF16>
+__device__ __forceinline__ void convert32(const uint4 &v, const ZeroScale<BF16> &zs, bool interleaved,
+                                          uint32_t (&out)[16]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint32_t p[4];
+        dequant8<BF16>(w[j], zs, p);  // p[i] = (nibble i, nibble i+4)
+        if (interleaved) {            // nibble order c0 c2 c4 c6 c1 c3 c5 c7: pairs are already (c0,c1)(c2,c3)..
+            out[4 * j + 0] = p[0];
+            out[4 * j + 1] = p[1];
+            out[4 * j + 2] = p[2];
+            out[4 * j + 3] = p[3];
+        } else {
+            out[4 * j + 0] = prmt(p[0], p[1], 0x5410u);
+            out[4 * j + 1] = prmt(p[2], p[3], 0x5410u);
+            out[4 * j + 2] = prmt(p[0], p[1], 0x7632u);
+            out[4 * j + 3] = prmt(p[2], p[3], 0x7632u);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// kernel
+// ---------------------------------------------------------------------------------------------
+template <bool BF16, int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, GemmCfg<BN>::CTAS_PER_SM)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+            const GemmParams p) {
+    using C = GemmCfg<BN>;
+    constexpr int BK = C::BK;
+    constexpr int STAGES = C::STAGES;
+    constexpr int NA = C::NA;
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+    __shared__ int s_is_last;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = smem_base + STAGES * C::STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto afull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto aempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + NA + a); };
+    const uint32_t dfull_bar = bar_base + 8u * (2 * STAGES + 2 * NA);
+    auto w_stage = [&](int s) { return smem_base + (uint32_t)s * C::STAGE_BYTES; };
+    auto x_stage = [&](int s) { return smem_base + (uint32_t)s * C::STAGE_BYTES + C::W_STAGE_BYTES; };
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int m_tile = blockIdx.x;
+    const int n_tile = blockIdx.y;
+    const int split = blockIdx.z;
+    const int kb0 = split * p.kblocks_per_split;
+    const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks);
+    const int nkb = kb1 - kb0;
+    const int64_t n0 = (int64_t)n_tile * 128;
+    const int64_t m0 = (int64_t)m_tile * BN;
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 128 + 1);
+        }
+        for (int a = 0; a < NA; ++a) {
+            mbar_init(afull_bar(a), 128);
+            mbar_init(aempty_bar(a), 1);
+        }
+        mbar_init(dfull_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8 && lane == 0) {
+        tma_prefetch_desc(&tmap_w);
+        tma_prefetch_desc(&tmap_x);
+    }
+    if (warp == 9) {
+        tmem_alloc(smem_u32(&s_tmem_base), C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+    volatile int *abort_flag = &s_abort;
+
+    int producer_issued = 0;
+    if (warp == 8) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            for (int it = 0; it < nkb; ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) break;
+                mbar_arrive_expect_tx(full_bar(s), C::STAGE_BYTES);
+                const int kb = kb0 + it;
+                tma_load_2d(w_stage(s), &tmap_w, full_bar(s), kb * C::W_ROW_BYTES, (int)n0);
+#pragma unroll
+                for (int b = 0; b < BK / 64; ++b)
+                    tma_load_2d(x_stage(s) + b * C::X_BOX_BYTES, &tmap_x, full_bar(s), kb * BK + b * 64, (int)m0);
+                producer_issued = it + 1;
+            }
+        }
+    } else if (warp == 9) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | ((BF16 ? 1u : 0u) << 7) | ((BF16 ? 1u : 0u) << 10) |
+                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            for (int it = 0; it < nkb; ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                const int a = it % NA;
+                const uint32_t aph = (it / NA) & 1;
+                if (!mbar_wait(full_bar(s), ph, abort_flag)) break;
+                if (!mbar_wait(afull_bar(a), aph, abort_flag)) break;
+                tc_fence_after();
+                const uint32_t a_tmem = tmem_base + BN + a * C::A_COLS;
+#pragma unroll
+                for (int kk = 0; kk < BK / 16; ++kk) {
+                    const uint64_t bdesc = make_b_desc(x_stage(s) + (kk >> 2) * C::X_BOX_BYTES + (kk & 3) * 32);
+                    umma_ts(tmem_base, a_tmem + kk * 8, bdesc, idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(empty_bar(s));
+                umma_commit(aempty_bar(a));
+                if (it == nkb - 1) umma_commit(dfull_bar);
+            }
+        }
+    } else {
+        // ------------------------------ converters ------------------------------
+        const int wg = warp >> 2;              // 0 or 1
+        const int row = tid & 127;             // TMEM lane and weight row inside the tile
+        const int64_t n = n0 + row;
+        const uint32_t lane_taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        const bool interleaved = p.interleaved != 0;
+        // swizzled 16-byte chunk positions of this row inside a weight stage
+        const uint32_t row_off = (uint32_t)row * C::W_ROW_BYTES;
+        const uint32_t sw = (BK == 128) ? ((row >> 1) & 3) : ((row >> 2) & 1);
+
+        int it = wg;
+        ZeroScale<BF16> zs;
+        if (it < nkb) {
+            const int64_t gi = ((int64_t)(kb0 + it) * BK) / p.group_size;
+            zs.set(load_zero_rt(p.zeros, p.zero_mode, p.zero_const, gi, n, p.N), __ldg(p.scales + gi * p.N + n));
+        }
+        for (; it < nkb; it += 2) {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            const int a = it % NA;
+            const uint32_t aph = (it / NA) & 1;
+            // constants of the next k-block of this group, requested before the waits
+            ZeroScale<BF16> zs_next = zs;
+            if (it + 2 < nkb) {
+                const int64_t gi = ((int64_t)(kb0 + it + 2) * BK) / p.group_size;
+                zs_next.set(load_zero_rt(p.zeros, p.zero_mode, p.zero_const, gi, n, p.N),
+                            __ldg(p.scales + gi * p.N + n));
+            }
+            // warp-uniform outcome: the tcgen05.st below is warp-collective
+            bool ready = mbar_wait(full_bar(s), ph, abort_flag);
+            ready = ready && mbar_wait(aempty_bar(a), aph ^ 1, abort_flag);
+            if (!__all_sync(0xffffffffu, ready)) break;
+            tc_fence_after();
+            const uint32_t wbase = w_stage(s) + row_off;
+            const uint32_t a_col = BN + a * C::A_COLS;
+#pragma unroll
+            for (int c = 0; c < C::W_ROW_BYTES / 16; ++c) {
+                const uint4 v = lds128(wbase + (((uint32_t)c ^ sw) << 4));
+                uint32_t out[16];
+                convert32<BF16>(v, zs, interleaved, out);
+                tmem_st16(lane_taddr + a_col + c * 16, out);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(afull_bar(a));
+            mbar_arrive(empty_bar(s));
+            zs = zs_next;
+        }
+
+        // ------------------------------ epilogue ------------------------------
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(dfull_bar, 0, abort_flag));
+        tc_fence_after();
+        if (ok) {
+            constexpr int COLS_PER_WG = BN / 2;
+            const int64_t Mp = (int64_t)gridDim.x * BN;
+#pragma unroll 1
+            for (int c8 = 0; c8 < COLS_PER_WG / 8; ++c8) {
+                const int col = wg * COLS_PER_WG + c8 * 8;
+                uint32_t r[8];
+                tmem_ld8(lane_taddr + col, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int64_t m = m0 + col + j;
+                    const float v = __uint_as_float(r[j]);
+                    if (p.split_k == 1) {
+                        if (m < p.M) store_out(p.Y, p.out_dtype, m * p.N + n, v);
+                    } else {
+                        __stcg(p.partial + ((int64_t)split * Mp + m) * p.N + n, v);
+                    }
+                }
+            }
+        }
+    }
+
+    // ------------------------------ teardown ------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (s_abort) {
+        if (warp == 8 && lane == 0) {
+            // drain this CTA's own TMA copies before the shared memory goes away
+            int dummy = 0;
+            volatile int *no_abort = &dummy;
+            for (int it = max(0, producer_issued - STAGES); it < producer_issued; ++it)
+                mbar_wait(full_bar(it % STAGES), (it / STAGES) & 1, no_abort);
+            atomicExch(p.status, QF_ERR_TIMEOUT);
+        }
+        __syncthreads();
+    } else if (p.split_k > 1) {
+        // split-K: last CTA of this (m_tile, n_tile) sums the partial tiles in split order
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            int *cnt = p.counters + (int64_t)n_tile * gridDim.x + m_tile;
+            const int prev = atomicAdd(cnt, 1);
+            s_is_last = (prev == p.split_k - 1);
+            if (s_is_last) *cnt = 0;
+        }
+        __syncthreads();
+        if (s_is_last) {
+            __threadfence();
+            const int64_t Mp = (int64_t)gridDim.x * BN;
+            for (int u = tid; u < 128 * BN; u += GEMM_THREADS) {
+                const int nl = u & 127;
+                const int64_t m = m0 + (u >> 7);
+                if (m < p.M) {
+                    float acc = 0.f;
+                    for (int sp = 0; sp < p.split_k; ++sp)
+                        acc += __ldcg(p.partial + ((int64_t)sp * Mp + m) * p.N + n0 + nl);
+                    store_out(p.Y, p.out_dtype, m * p.N + n0 + nl, acc);
+                }
+            }
+        }
+    }
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+static std::once_flag g_encode_once;
+
+static EncodeTiledFn get_encode() {
+    std::call_once(g_encode_once, [] {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            g_encode = (EncodeTiledFn)fn;
+    });
+    return g_encode;
+}
+
+struct MapKey {
+    const void *ptr;
+    uint64_t d0, d1;
+    uint32_t b0, b1;
+    int kind;
+    bool operator==(const MapKey &o) const {
+        return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && b0 == o.b0 && b1 == o.b1 && kind == o.kind;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey &k) const {
+        size_t h = std::hash<const void *>()(k.ptr);
+        h ^= std::hash<uint64_t>()(k.d0 * 1000003u + k.d1) + 0x9e3779b97f4a7c15ULL + (h << 6) + (h >> 2);
+        h ^= std::hash<uint64_t>()(((uint64_t)k.b0 << 32) | k.b1 | ((uint64_t)k.kind << 60)) + (h << 6) + (h >> 2);
+        return h;
+    }
+};
+static std::mutex g_map_mutex;
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+// 2-D row-major tensor map. kind 0: bytes (packed weights), 1: 16-bit elements (activations).
+static int get_tensor_map(qf_ctx *ctx, CUtensorMap *out, const void *ptr, int kind, uint64_t inner, uint64_t outer,
+                          uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz) {
+    MapKey key{ptr, inner, outer, box_inner, box_outer, kind * 8 + (int)swz};
+    {
+        std::lock_guard<std::mutex> g(g_map_mutex);
+        auto itf = g_maps.find(key);
+        if (itf != g_maps.end()) {
+            *out = itf->second;
+            return QF_OK;
+        }
+    }
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return fail(ctx, QF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const uint64_t esize = kind == 0 ? 1 : 2;
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {inner * esize};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(out, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2,
+                     const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ctx, QF_ERR_CUDA, "cuTensorMapEncodeTiled failed (" + std::to_string((int)r) + ")");
+    std::lock_guard<std::mutex> g(g_map_mutex);
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps[key] = *out;
+    return QF_OK;
+}
+
+template <bool BF16, int BN>
+static cudaError_t gemm_set_attr() {
+    return cudaFuncSetAttribute(gemm_kernel<BF16, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                GemmCfg<BN>::SMEM_BYTES);
+}
+
+int gemm_init(qf_ctx *ctx) {
+    QF_CUDA_TRY(ctx, (gemm_set_attr<false, 16>()));
+    QF_CUDA_TRY(ctx, (gemm_set_attr<false, 32>()));
+    QF_CUDA_TRY(ctx, (gemm_set_attr<false, 64>()));
+    QF_CUDA_TRY(ctx, (gemm_set_attr<false, 128>()));
+    QF_CUDA_TRY(ctx, (gemm_set_attr<false, 256>()));
+    QF_CUDA_TRY(ctx, (gemm_set_attr<true, 16>()));
+    QF_CUDA_TRY(ctx, (gemm_set_attr<true, 32>()));
+    QF_CUDA_TRY(ctx, (gemm_set_attr<true, 64>()));
+    QF_CUDA_TRY(ctx, (gemm_set_attr<true, 128>()));
+    QF_CUDA_TRY(ctx, (gemm_set_attr<true, 256>()));
+    if (!ctx->host_status) {
+        QF_CUDA_TRY(ctx, cudaHostAlloc((void **)&ctx->host_status, sizeof(int), cudaHostAllocMapped));
+        *ctx->host_status = 0;
+        QF_CUDA_TRY(ctx, cudaHostGetDevicePointer((void **)&ctx->dev_status, ctx->host_status, 0));
+    }
+    return QF_OK;
+}
+
+template <bool BF16, int BN>
+static int gemm_launch_bn(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
+                          GemmParams &p, cudaStream_t s) {
+    using C = GemmCfg<BN>;
+    CUtensorMap tw, tx;
+    int st = get_tensor_map(ctx, &tw, qw, 0, (uint64_t)d->K / 2, (uint64_t)d->N, C::W_ROW_BYTES, 128,
+                            C::BK == 128 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    if (st != QF_OK) return st;
+    st = get_tensor_map(ctx, &tx, X, 1, (uint64_t)d->K, (uint64_t)d->M, 64, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != QF_OK) return st;
+    p.kblocks = (int)(d->K / C::BK);
+    p.kblocks_per_split = plan.chunks_per_split;
+    dim3 grid((unsigned)plan.m_tiles, (unsigned)(d->N / 128), (unsigned)plan.split_k);
+    gemm_kernel<BF16, BN><<<grid, GEMM_THREADS, C::SMEM_BYTES, s>>>(tw, tx, p);
+    g_launch_count.fetch_add(1);
+    QF_CUDA_TRY(ctx, cudaGetLastError());
+    return QF_OK;
+}
+
+template <bool BF16>
+static int gemm_launch_dt(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
+                          GemmParams &p, cudaStream_t s) {
+    switch (plan.bn) {
+        case 16: return gemm_launch_bn<BF16, 16>(ctx, d, plan, X, qw, p, s);
+        case 32: return gemm_launch_bn<BF16, 32>(ctx, d, plan, X, qw, p, s);
+        case 64: return gemm_launch_bn<BF16, 64>(ctx, d, plan, X, qw, p, s);
+        case 128: return gemm_launch_bn<BF16, 128>(ctx, d, plan, X, qw, p, s);
+        case 256: return gemm_launch_bn<BF16, 256>(ctx, d, plan, X, qw, p, s);
+        default: return fail(ctx, QF_ERR_BAD_ARG, "bad batch tile");
+    }
+}
+
+int gemm_block_k(int bn) { return bn <= 128 ? 128 : 64; }
+
+int launch_gemm(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
+                const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s) {
+    GemmParams p;
+    p.scales = (const uint16_t *)scales;
+    p.zeros = zeros;
+    p.Y = Y;
+    p.counters = (int *)ws;
+    p.partial = (float *)((char *)ws + plan.ws_counter_bytes);
+    p.status = ctx->dev_status;
+    p.M = d->M;
+    p.N = d->N;
+    p.K = d->K;
+    p.group_size = d->group_size;
+    p.zero_mode = d->zero_mode;
+    p.zero_const = d->zero_const;
+    p.out_dtype = d->out_dtype;
+    p.split_k = plan.split_k;
+    p.interleaved = d->weight_layout == QF_LAYOUT_INTERLEAVED;
+    if (d->act_dtype == QF_BF16) return gemm_launch_dt<true>(ctx, d, plan, X, qw, p, s);
+    return gemm_launch_dt<false>(ctx, d, plan, X, qw, p, s);
+}
+
 }  // namespace qf

@@ -103,7 +103,7 @@ __device__ __forceinline__ void load_batch(WBatch &b, const GemvParams &p, int64
 }
 
 template <bool BF16>
-__device__ __forceinline__ void compute_batch(const WBatch &b, float (&acc)[4], const uint4 *xs, int c_local_begin,
+__device__ __forceinline__ void compute_batch(const WBatch &b, float (&acc)[2][4], const uint4 *xs, int c_local_begin,
                                               int n_valid, int lane) {
 #pragma unroll
     for (int i = 0; i < GEMV_CB; ++i) {
@@ -120,8 +120,8 @@ __device__ __forceinline__ void compute_batch(const WBatch &b, float (&acc)[4], 
                 dequant8<BF16>(wa[j], za, pa);
                 dequant8<BF16>(wb[j], zb, pb);
                 const uint4 xb = xc[j * 32];
-                mma_16816<BF16>(acc, pa[0], pb[0], pa[1], pb[1], xb.x, xb.y);
-                mma_16816<BF16>(acc, pa[2], pb[2], pa[3], pb[3], xb.z, xb.w);
+                mma_16816<BF16>(acc[0], pa[0], pb[0], pa[1], pb[1], xb.x, xb.y);
+                mma_16816<BF16>(acc[1], pa[2], pb[2], pa[3], pb[3], xb.z, xb.w);
             }
         }
     }
@@ -173,20 +173,23 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
     __syncthreads();
 
     // 3. main loop, register double buffering
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // two chains: MMAs of one chain are dependent
     if (warp_active) {
         for (int c = c0; c < c1; c += 2 * GEMV_CB) {
             const bool has_b = (c + GEMV_CB) < c1;
             if (has_b) load_batch<ZMODE>(B, p, row_a, c + GEMV_CB, c1, t);
-            compute_batch<BF16>(A, acc, xs, c - c0, min(GEMV_CB, c1 - c), lane);
+            compute_batch<BF16>(A, acc2, xs, c - c0, min(GEMV_CB, c1 - c), lane);
             if (has_b) {
                 if (c + 2 * GEMV_CB < c1) load_batch<ZMODE>(A, p, row_a, c + 2 * GEMV_CB, c1, t);
-                compute_batch<BF16>(B, acc, xs, c + GEMV_CB - c0, min(GEMV_CB, c1 - c - GEMV_CB), lane);
+                compute_batch<BF16>(B, acc2, xs, c + GEMV_CB - c0, min(GEMV_CB, c1 - c - GEMV_CB), lane);
             }
         }
     }
 
     // 4. epilogue. acc[0..1]: row g, batch 2t, 2t+1 ; acc[2..3]: row g+8
+    float acc[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = acc2[0][i] + acc2[1][i];
     const int64_t m0 = (int64_t)mt * 8 + 2 * t;
     if (p.split_k == 1) {
         if (warp_active) {
@@ -268,8 +271,8 @@ int launch_gemv(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const vo
     p.scales = (const uint16_t *)scales;
     p.zeros = zeros;
     p.Y = Y;
-    p.partial = (float *)ws;
-    p.counters = (int *)((char *)ws + plan.ws_partial_bytes);
+    p.counters = (int *)ws;  // fixed-size counter region first, partial sums after it
+    p.partial = (float *)((char *)ws + plan.ws_counter_bytes);
     p.M = d->M;
     p.N = d->N;
     p.K = d->K;

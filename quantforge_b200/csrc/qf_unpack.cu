@@ -69,6 +69,44 @@ int launch_unpack(qf_ctx *ctx, const void *packed, void *out, int64_t rows, int6
     return QF_OK;
 }
 
+// Nibble permutation inside each word. canonical nibbles c0..c7 -> interleaved c0 c2 c4 c6 c1 c3 c5 c7.
+__device__ __forceinline__ uint32_t interleave_word(uint32_t w) {
+    uint32_t r = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        r |= ((w >> (8 * i)) & 0xFu) << (4 * i);            // even codes -> nibbles 0..3
+        r |= ((w >> (8 * i + 4)) & 0xFu) << (4 * (i + 4));  // odd codes  -> nibbles 4..7
+    }
+    return r;
+}
+__device__ __forceinline__ uint32_t deinterleave_word(uint32_t w) {
+    uint32_t r = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        r |= ((w >> (4 * i)) & 0xFu) << (8 * i);
+        r |= ((w >> (4 * (i + 4))) & 0xFu) << (8 * i + 4);
+    }
+    return r;
+}
+
+__global__ void __launch_bounds__(256) prepack_kernel(const uint32_t *__restrict__ in, uint32_t *__restrict__ out,
+                                                      int64_t n_words, int to_canonical) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += stride) {
+        const uint32_t w = in[i];
+        out[i] = to_canonical ? deinterleave_word(w) : interleave_word(w);
+    }
+}
+
+int launch_prepack(qf_ctx *ctx, const void *in, void *out, int64_t n_words, int to_canonical, cudaStream_t s) {
+    int64_t blocks = (n_words + 255) / 256;
+    if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
+    prepack_kernel<<<(unsigned)blocks, 256, 0, s>>>((const uint32_t *)in, (uint32_t *)out, n_words, to_canonical);
+    g_launch_count.fetch_add(1);
+    QF_CUDA_TRY(ctx, cudaGetLastError());
+    return QF_OK;
+}
+
 // One thread per packed word (8 codes along K of one row).
 template <bool BF16, int ZMODE>
 __global__ void __launch_bounds__(256) dequant_kernel(const uint32_t *__restrict__ qw,

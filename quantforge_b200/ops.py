@@ -13,8 +13,8 @@ from typing import Optional
 import torch
 
 from . import _lib
-from ._lib import (QF_BF16, QF_F16, QF_F32, QF_PATH_AUTO, QF_ZERO_CONST, QF_ZERO_I8, QF_ZERO_U4, LinearDesc,
-                   QuantForgeError)
+from ._lib import (QF_BF16, QF_F16, QF_F32, QF_LAYOUT_CANONICAL, QF_LAYOUT_INTERLEAVED, QF_PATH_AUTO, QF_ZERO_CONST,
+                   QF_ZERO_I8, QF_ZERO_U4, LinearDesc, QuantForgeError)
 
 _DT = {torch.float16: QF_F16, torch.bfloat16: QF_BF16, torch.float32: QF_F32}
 _ctxs: dict[int, ctypes.c_void_p] = {}
@@ -110,7 +110,8 @@ def unpack_int4(packed: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------------------------
 # linear
 # --------------------------------------------------------------------------------------------
-def _make_desc(M, N, K, group_size, act_dtype, out_dtype, zeros, zero_const, path, split_k) -> LinearDesc:
+def _make_desc(M, N, K, group_size, act_dtype, out_dtype, zeros, zero_const, path, split_k,
+               weight_layout=QF_LAYOUT_CANONICAL) -> LinearDesc:
     d = LinearDesc()
     d.M, d.N, d.K = M, N, K
     d.group_size = group_size
@@ -126,6 +127,7 @@ def _make_desc(M, N, K, group_size, act_dtype, out_dtype, zeros, zero_const, pat
         raise TypeError("zeros must be None (constant), int8 [G,N] or packed int32 [G,N/8]")
     d.path = path
     d.split_k = split_k
+    d.weight_layout = weight_layout
     return d
 
 
@@ -174,8 +176,11 @@ def _check_linear_tensors(x, qweight, scales, zeros, group_size):
 
 def w4a16_linear(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor] = None,
                  group_size: int = 128, zero_const: int = 8, out_dtype: Optional[torch.dtype] = None,
-                 path: int = QF_PATH_AUTO, split_k: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 path: int = QF_PATH_AUTO, split_k: int = 0, out: Optional[torch.Tensor] = None,
+                 weight_layout: int = QF_LAYOUT_CANONICAL) -> torch.Tensor:
     """Y[M,N] = X[M,K] . dequant(unpack(qweight))^T, fp32 accumulation, W never materialised.
+
+    weight_layout: QF_LAYOUT_CANONICAL, or QF_LAYOUT_INTERLEAVED for weights passed through prepack_w4.
 
     x        f16|bf16 [M, K]
     qweight  int8 [N, K/2] (two codes per byte along K) or int32 [N, K/8]
@@ -191,7 +196,7 @@ def w4a16_linear(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, z
         out = torch.empty((M, N), dtype=out_dtype, device=dev)
     elif tuple(out.shape) != (M, N) or out.dtype != out_dtype or not out.is_contiguous():
         raise ValueError("out must be a contiguous [M, N] tensor of out_dtype")
-    d = _make_desc(M, N, K, group_size, x.dtype, out_dtype, zeros, zero_const, path, split_k)
+    d = _make_desc(M, N, K, group_size, x.dtype, out_dtype, zeros, zero_const, path, split_k, weight_layout)
     ctx = _ctx(dev)
     with torch.cuda.device(dev):
         ws = _workspace(dev, workspace_bytes(d))
@@ -204,7 +209,7 @@ def w4a16_linear(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, z
 def w4a16_linear_host(x_host: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
                       zeros: Optional[torch.Tensor] = None, group_size: int = 128, zero_const: int = 8,
                       out_dtype: Optional[torch.dtype] = None, out_host: Optional[torch.Tensor] = None,
-                      path: int = QF_PATH_AUTO) -> torch.Tensor:
+                      path: int = QF_PATH_AUTO, weight_layout: int = QF_LAYOUT_CANONICAL) -> torch.Tensor:
     """Same linear with activations and result in HOST memory (pinned for speed); weights stay on the GPU."""
     if x_host.is_cuda:
         raise ValueError("x_host must be a CPU tensor")
@@ -214,7 +219,7 @@ def w4a16_linear_host(x_host: torch.Tensor, qweight: torch.Tensor, scales: torch
     x_host = x_host.contiguous()
     if out_host is None:
         out_host = torch.empty((M, N), dtype=out_dtype, pin_memory=True)
-    d = _make_desc(M, N, K, group_size, x_host.dtype, out_dtype, zeros, zero_const, path, 0)
+    d = _make_desc(M, N, K, group_size, x_host.dtype, out_dtype, zeros, zero_const, path, 0, weight_layout)
     ctx = _ctx(dev)
     with torch.cuda.device(dev):
         ws = _workspace(dev, workspace_bytes(d))
@@ -243,6 +248,34 @@ def dequant_w4(qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torc
     return out
 
 
+def prepack_w4(qweight: torch.Tensor, to_canonical: bool = False) -> torch.Tensor:
+    """One-time permutation of the nibbles inside each 32-bit word: canonical -> QF_LAYOUT_INTERLEAVED (or back)."""
+    dev = _need_cuda(qweight)
+    qweight = qweight.contiguous()
+    nbytes = qweight.numel() * qweight.element_size()
+    if nbytes % 4 != 0:
+        raise ValueError("qweight must hold whole 32-bit words")
+    out = torch.empty_like(qweight)
+    ctx = _ctx(dev)
+    with torch.cuda.device(dev):
+        st = _lib.load().qf_prepack_w4(ctx, _ptr(qweight), _ptr(out), nbytes // 4, 1 if to_canonical else 0,
+                                       _stream(dev))
+    _check(st, ctx)
+    return out
+
+
+def device_status(device: Optional[torch.device] = None) -> int:
+    """Sticky device-side status of the context (0, or QF_ERR_TIMEOUT after a bounded wait expired). Synchronises."""
+    dev = device or torch.device("cuda", torch.cuda.current_device())
+    torch.cuda.synchronize(dev)
+    return int(_lib.load().qf_ctx_status(_ctx(dev)))
+
+
+def clear_device_status(device: Optional[torch.device] = None) -> None:
+    dev = device or torch.device("cuda", torch.cuda.current_device())
+    _lib.load().qf_ctx_clear_status(_ctx(dev))
+
+
 def gemv_int4(x: torch.Tensor, w_packed: torch.Tensor, scale: torch.Tensor, zero_point: torch.Tensor) -> torch.Tensor:
     """Drop-in for the reference's `gemv_int4_baseline(x, w_packed, scale, zero_point)`.
 
@@ -258,14 +291,18 @@ class W4A16Linear:
     """A quantised linear layer whose weights live on one GPU: y = x . W^T."""
 
     def __init__(self, qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor] = None,
-                 group_size: int = 128, zero_const: int = 8):
+                 group_size: int = 128, zero_const: int = 8, prepack: bool = False):
         _need_cuda(qweight, scales, zeros)
         self.qweight, self.scales, self.zeros = qweight.contiguous(), scales.contiguous(), zeros
         self.group_size, self.zero_const = group_size, zero_const
+        self.weight_layout = QF_LAYOUT_CANONICAL
+        if prepack and qweight.shape[0] % 128 == 0:
+            self.qweight = prepack_w4(self.qweight)
+            self.weight_layout = QF_LAYOUT_INTERLEAVED
         self.N = qweight.shape[0]
         self.K = qweight.shape[1] * (8 if qweight.dtype == torch.int32 else 2)
 
     def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
         return w4a16_linear(x, self.qweight, self.scales, self.zeros, self.group_size, self.zero_const, out_dtype,
-                            out=out)
+                            out=out, weight_layout=self.weight_layout)
