@@ -56,9 +56,17 @@ typedef enum qf_path { QF_PATH_AUTO = 0, QF_PATH_GEMV = 1, QF_PATH_GEMM = 2 } qf
  *   QF_LAYOUT_CANONICAL   : nibble i holds code 8j+i (what qf.unpack defines; lib/Transforms/LowerUnpackToNVVM.cpp:254-265)
  *   QF_LAYOUT_INTERLEAVED : nibbles hold codes 8j + {0,2,4,6,1,3,5,7}; produced once by qf_prepack_w4. With it the
  *                           lop3 converter yields (k, k+1) pairs directly and the GEMM kernel skips a byte permute.
- * Rows, words per row and everything else are unchanged: the prepack is a pure permutation inside each word.
+ *                           Rows and words per row are unchanged: a pure permutation inside each word.
+ *   QF_LAYOUT_TILED       : INTERLEAVED words regrouped so that the 128 rows x 128 codes (8 KB) a thread block
+ *                           consumes per pipeline step are contiguous in HBM: word w (0..15) of row r (0..127) of
+ *                           k-block kb of row tile nt sits at word index ((nt * K/128 + kb) * 128 + r) * 16 + w.
+ *                           Needs N % 128 == 0. Produced once by qf_prepack_w4_tiled.
  */
-typedef enum qf_weight_layout { QF_LAYOUT_CANONICAL = 0, QF_LAYOUT_INTERLEAVED = 1 } qf_weight_layout;
+typedef enum qf_weight_layout {
+    QF_LAYOUT_CANONICAL = 0,
+    QF_LAYOUT_INTERLEAVED = 1,
+    QF_LAYOUT_TILED = 2
+} qf_weight_layout;
 
 typedef struct qf_ctx qf_ctx;
 
@@ -136,6 +144,9 @@ int qf_w4a16_linear_host(qf_ctx *ctx, const qf_linear_desc *desc, const void *X_
  */
 int qf_prepack_w4(qf_ctx *ctx, const void *qweight_in, void *qweight_out, int64_t n_words, int to_canonical,
                   void *stream);
+/* canonical [N, K/8] words -> QF_LAYOUT_TILED (or back with to_canonical != 0). in and out must not alias. */
+int qf_prepack_w4_tiled(qf_ctx *ctx, const void *qweight_in, void *qweight_out, int64_t N, int64_t K,
+                        int to_canonical, void *stream);
 
 /*
  * Sticky device-side status of this context: QF_OK, or QF_ERR_TIMEOUT when a kernel's bounded wait expired

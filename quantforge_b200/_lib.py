@@ -15,13 +15,13 @@ QF_OK = 0
 QF_F16, QF_BF16, QF_F32 = 0, 1, 2
 QF_ZERO_CONST, QF_ZERO_U4, QF_ZERO_I8 = 0, 1, 2
 QF_PATH_AUTO, QF_PATH_GEMV, QF_PATH_GEMM = 0, 1, 2
-QF_LAYOUT_CANONICAL, QF_LAYOUT_INTERLEAVED = 0, 1
+QF_LAYOUT_CANONICAL, QF_LAYOUT_INTERLEAVED, QF_LAYOUT_TILED = 0, 1, 2
 
 # every symbol include/quantforge_rt.h declares
 EXPORTS = [
     "qf_version", "qf_status_string", "qf_ctx_create", "qf_ctx_destroy", "qf_last_error", "qf_unpack_int4",
     "qf_dequant_w4", "qf_w4a16_workspace_bytes", "qf_w4a16_linear", "qf_w4a16_linear_host", "qf_w4a16_plan",
-    "qf_launch_count", "qf_prepack_w4", "qf_ctx_status", "qf_ctx_clear_status",
+    "qf_launch_count", "qf_prepack_w4", "qf_prepack_w4_tiled", "qf_ctx_status", "qf_ctx_clear_status",
 ]
 
 
@@ -72,6 +72,7 @@ def load() -> ctypes.CDLL:
     lib.qf_w4a16_plan.argtypes = [dp, ctypes.POINTER(i32), ctypes.POINTER(i32)]
     lib.qf_launch_count.restype = i64
     lib.qf_prepack_w4.argtypes = [vp, vp, vp, i64, ctypes.c_int, vp]
+    lib.qf_prepack_w4_tiled.argtypes = [vp, vp, vp, i64, i64, ctypes.c_int, vp]
     lib.qf_ctx_status.argtypes = [vp]
     lib.qf_ctx_clear_status.argtypes = [vp]
     _lib = lib

@@ -36,7 +36,8 @@ int make_plan(const qf_linear_desc *d, Plan *p, std::string *why) {
     if (d->zero_mode == QF_ZERO_CONST && (d->zero_const < -128 || d->zero_const > 127))
         return bad(QF_ERR_BAD_ARG, "zero_const must fit a signed 8-bit zero point");
     if (d->split_k < 0) return bad(QF_ERR_BAD_ARG, "split_k must be >= 0");
-    if (d->weight_layout != QF_LAYOUT_CANONICAL && d->weight_layout != QF_LAYOUT_INTERLEAVED)
+    if (d->weight_layout != QF_LAYOUT_CANONICAL && d->weight_layout != QF_LAYOUT_INTERLEAVED &&
+        d->weight_layout != QF_LAYOUT_TILED)
         return bad(QF_ERR_BAD_ARG, "unknown weight_layout");
     for (int i = 0; i < 4; ++i)
         if (d->reserved[i] != 0) return bad(QF_ERR_BAD_ARG, "reserved fields must be zero");
@@ -306,6 +307,18 @@ int qf_prepack_w4(qf_ctx *ctx, const void *qweight_in, void *qweight_out, int64_
     if (((uintptr_t)qweight_in & 3u) || ((uintptr_t)qweight_out & 3u))
         return fail(ctx, QF_ERR_BAD_ARG, "weights must be 4-byte aligned");
     return launch_prepack(ctx, qweight_in, qweight_out, n_words, to_canonical, (cudaStream_t)stream);
+}
+
+int qf_prepack_w4_tiled(qf_ctx *ctx, const void *qweight_in, void *qweight_out, int64_t N, int64_t K,
+                        int to_canonical, void *stream) {
+    if (!ctx) return QF_ERR_BAD_ARG;
+    if (N <= 0 || K <= 0 || N % 128 != 0 || K % 128 != 0)
+        return fail(ctx, QF_ERR_BAD_ARG, "the tiled layout needs N and K to be multiples of 128");
+    if (!qweight_in || !qweight_out) return fail(ctx, QF_ERR_BAD_ARG, "null tensor pointer");
+    if (qweight_in == qweight_out) return fail(ctx, QF_ERR_BAD_ARG, "in and out must not alias");
+    if (((uintptr_t)qweight_in & 15u) || ((uintptr_t)qweight_out & 15u))
+        return fail(ctx, QF_ERR_BAD_ARG, "weights must be 16-byte aligned");
+    return launch_prepack_tiled(ctx, qweight_in, qweight_out, N, K, to_canonical, (cudaStream_t)stream);
 }
 
 int qf_ctx_status(const qf_ctx *ctx) {

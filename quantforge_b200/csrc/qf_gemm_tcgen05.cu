@@ -44,7 +44,9 @@ struct GemmCfg {
     static constexpr int A_COLS = BK / 2;                        // 32-bit TMEM columns per A buffer
     static constexpr int TMEM_COLS = (BN + NA * A_COLS) <= 256 ? 256 : 512;
     static constexpr int CTAS_PER_SM = BN <= 64 ? 2 : 1;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int SZ_BYTES = 512;                          // per stage: 256 B scales + up to 128 B zeros
+    static constexpr int SMEM_BYTES =
+        STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + STAGES * SZ_BYTES;
 };
 
 constexpr int GEMM_THREADS = 320;
@@ -65,6 +67,7 @@ struct GemmParams {
     int kblocks_per_split;
     int split_k;
     int interleaved;       // weight nibble order inside a word: 0 canonical, 1 pair-interleaved
+    int tiled;             // 1: weights stored tile-major (QF_LAYOUT_TILED)
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -116,6 +119,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
+}
+// Untiled bulk copy global -> shared (16-byte aligned, size a multiple of 16), completion on an mbarrier.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -238,6 +247,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
     const uint32_t dfull_bar = bar_base + 8u * (2 * STAGES + 2 * NA);
     auto w_stage = [&](int s) { return smem_base + (uint32_t)s * C::STAGE_BYTES; };
     auto x_stage = [&](int s) { return smem_base + (uint32_t)s * C::STAGE_BYTES + C::W_STAGE_BYTES; };
+    auto sz_stage = [&](int s) { return bar_base + 256u + (uint32_t)s * C::SZ_BYTES; };
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -286,9 +296,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
                 if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) break;
-                mbar_arrive_expect_tx(full_bar(s), C::STAGE_BYTES);
                 const int kb = kb0 + it;
-                tma_load_2d(w_stage(s), &tmap_w, full_bar(s), kb * C::W_ROW_BYTES, (int)n0);
+                const int64_t gi = ((int64_t)kb * BK) / p.group_size;
+                const uint32_t zbytes = p.zero_mode == QF_ZERO_U4 ? 64u : p.zero_mode == QF_ZERO_I8 ? 128u : 0u;
+                mbar_arrive_expect_tx(full_bar(s), C::STAGE_BYTES + 256u + zbytes);
+                bulk_load(sz_stage(s), p.scales + gi * p.N + n0, 256u, full_bar(s));
+                if (p.zero_mode == QF_ZERO_U4)
+                    bulk_load(sz_stage(s) + 256u, (const uint8_t *)p.zeros + (gi * p.N + n0) / 2, 64u, full_bar(s));
+                else if (p.zero_mode == QF_ZERO_I8)
+                    bulk_load(sz_stage(s) + 256u, (const uint8_t *)p.zeros + gi * p.N + n0, 128u, full_bar(s));
+                if (p.tiled) {
+                    // tile-major weights: rows of 64 bytes, the 128 rows of (n_tile, 128-code block) adjacent
+                    const int kb128 = (kb * BK) >> 7;
+                    const int c0 = (BK == 128) ? 0 : (kb & 1) * 32;
+                    tma_load_2d(w_stage(s), &tmap_w, full_bar(s), c0, (n_tile * (int)(p.K >> 7) + kb128) * 128);
+                } else {
+                    tma_load_2d(w_stage(s), &tmap_w, full_bar(s), kb * C::W_ROW_BYTES, (int)n0);
+                }
 #pragma unroll
                 for (int b = 0; b < BK / 64; ++b)
                     tma_load_2d(x_stage(s) + b * C::X_BOX_BYTES, &tmap_x, full_bar(s), kb * BK + b * 64, (int)m0);
@@ -330,29 +354,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
         const uint32_t row_off = (uint32_t)row * C::W_ROW_BYTES;
         const uint32_t sw = (BK == 128) ? ((row >> 1) & 3) : ((row >> 2) & 1);
 
-        int it = wg;
-        ZeroScale<BF16> zs;
-        if (it < nkb) {
-            const int64_t gi = ((int64_t)(kb0 + it) * BK) / p.group_size;
-            zs.set(load_zero_rt(p.zeros, p.zero_mode, p.zero_const, gi, n, p.N), __ldg(p.scales + gi * p.N + n));
-        }
-        for (; it < nkb; it += 2) {
+        for (int it = wg; it < nkb; it += 2) {
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1;
             const int a = it % NA;
             const uint32_t aph = (it / NA) & 1;
-            // constants of the next k-block of this group, requested before the waits
-            ZeroScale<BF16> zs_next = zs;
-            if (it + 2 < nkb) {
-                const int64_t gi = ((int64_t)(kb0 + it + 2) * BK) / p.group_size;
-                zs_next.set(load_zero_rt(p.zeros, p.zero_mode, p.zero_const, gi, n, p.N),
-                            __ldg(p.scales + gi * p.N + n));
-            }
             // warp-uniform outcome: the tcgen05.st below is warp-collective
             bool ready = mbar_wait(full_bar(s), ph, abort_flag);
             ready = ready && mbar_wait(aempty_bar(a), aph ^ 1, abort_flag);
             if (!__all_sync(0xffffffffu, ready)) break;
             tc_fence_after();
+            // zero and scale of (this row, this k-block's group) from the stage's slivers
+            ZeroScale<BF16> zs;
+            {
+                const uint32_t szb = sz_stage(s);
+                uint32_t sbits;
+                asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sbits) : "r"(szb + 2u * row));
+                int z = p.zero_const;
+                if (p.zero_mode == QF_ZERO_U4) {
+                    uint32_t zw;
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zw) : "r"(szb + 256u + 4u * (row >> 3)));
+                    z = (int)((zw >> (4 * (row & 7))) & 0xFu);
+                } else if (p.zero_mode == QF_ZERO_I8) {
+                    asm volatile("ld.shared.s8 %0, [%1];" : "=r"(z) : "r"(szb + 256u + row));
+                }
+                zs.set(z, sbits);
+            }
             const uint32_t wbase = w_stage(s) + row_off;
             const uint32_t a_col = BN + a * C::A_COLS;
 #pragma unroll
@@ -366,7 +393,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
             tc_fence_before();
             mbar_arrive(afull_bar(a));
             mbar_arrive(empty_bar(s));
-            zs = zs_next;
         }
 
         // ------------------------------ epilogue ------------------------------
@@ -539,7 +565,9 @@ static int gemm_launch_bn(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan
                           GemmParams &p, cudaStream_t s) {
     using C = GemmCfg<BN>;
     CUtensorMap tw, tx;
-    int st = get_tensor_map(ctx, &tw, qw, 0, (uint64_t)d->K / 2, (uint64_t)d->N, C::W_ROW_BYTES, 128,
+    const bool tiled = d->weight_layout == QF_LAYOUT_TILED;
+    int st = get_tensor_map(ctx, &tw, qw, 0, tiled ? 64 : (uint64_t)d->K / 2,
+                            tiled ? (uint64_t)d->N * (uint64_t)(d->K / 128) : (uint64_t)d->N, C::W_ROW_BYTES, 128,
                             C::BK == 128 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
     if (st != QF_OK) return st;
     st = get_tensor_map(ctx, &tx, X, 1, (uint64_t)d->K, (uint64_t)d->M, 64, BN, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -585,7 +613,8 @@ int launch_gemm(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const vo
     p.zero_const = d->zero_const;
     p.out_dtype = d->out_dtype;
     p.split_k = plan.split_k;
-    p.interleaved = d->weight_layout == QF_LAYOUT_INTERLEAVED;
+    p.interleaved = d->weight_layout != QF_LAYOUT_CANONICAL;
+    p.tiled = d->weight_layout == QF_LAYOUT_TILED;
     if (d->act_dtype == QF_BF16) return gemm_launch_dt<true>(ctx, d, plan, X, qw, p, s);
     return gemm_launch_dt<false>(ctx, d, plan, X, qw, p, s);
 }

@@ -107,6 +107,40 @@ int launch_prepack(qf_ctx *ctx, const void *in, void *out, int64_t n_words, int 
     return QF_OK;
 }
 
+// canonical word (n, j) <-> tiled word ((nt * KB + kb) * 128 + r) * 16 + w, n = nt*128 + r, j = kb*16 + w.
+__global__ void __launch_bounds__(256) prepack_tiled_kernel(const uint32_t *__restrict__ in,
+                                                            uint32_t *__restrict__ out, int64_t N, int64_t K,
+                                                            int to_canonical) {
+    const int64_t words_per_row = K >> 3;
+    const int64_t KB = K >> 7;
+    const int64_t total = N * words_per_row;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        // i enumerates the TILED order so that the side written (or read) in bulk is contiguous
+        const int64_t w = i & 15;
+        const int64_t r = (i >> 4) & 127;
+        const int64_t blk = i >> 11;
+        const int64_t kb = blk % KB;
+        const int64_t nt = blk / KB;
+        const int64_t canon = (nt * 128 + r) * words_per_row + kb * 16 + w;
+        if (to_canonical)
+            out[canon] = deinterleave_word(in[i]);
+        else
+            out[i] = interleave_word(in[canon]);
+    }
+}
+
+int launch_prepack_tiled(qf_ctx *ctx, const void *in, void *out, int64_t N, int64_t K, int to_canonical,
+                         cudaStream_t s) {
+    const int64_t total = N * (K / 8);
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
+    prepack_tiled_kernel<<<(unsigned)blocks, 256, 0, s>>>((const uint32_t *)in, (uint32_t *)out, N, K, to_canonical);
+    g_launch_count.fetch_add(1);
+    QF_CUDA_TRY(ctx, cudaGetLastError());
+    return QF_OK;
+}
+
 // One thread per packed word (8 codes along K of one row).
 template <bool BF16, int ZMODE>
 __global__ void __launch_bounds__(256) dequant_kernel(const uint32_t *__restrict__ qw,

@@ -13,8 +13,8 @@ from typing import Optional
 import torch
 
 from . import _lib
-from ._lib import (QF_BF16, QF_F16, QF_F32, QF_LAYOUT_CANONICAL, QF_LAYOUT_INTERLEAVED, QF_PATH_AUTO, QF_ZERO_CONST,
-                   QF_ZERO_I8, QF_ZERO_U4, LinearDesc, QuantForgeError)
+from ._lib import (QF_BF16, QF_F16, QF_F32, QF_LAYOUT_CANONICAL, QF_LAYOUT_INTERLEAVED, QF_LAYOUT_TILED, QF_PATH_AUTO,
+                   QF_ZERO_CONST, QF_ZERO_I8, QF_ZERO_U4, LinearDesc, QuantForgeError)
 
 _DT = {torch.float16: QF_F16, torch.bfloat16: QF_BF16, torch.float32: QF_F32}
 _ctxs: dict[int, ctypes.c_void_p] = {}
@@ -248,10 +248,23 @@ def dequant_w4(qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torc
     return out
 
 
-def prepack_w4(qweight: torch.Tensor, to_canonical: bool = False) -> torch.Tensor:
-    """One-time permutation of the nibbles inside each 32-bit word: canonical -> QF_LAYOUT_INTERLEAVED (or back)."""
+def prepack_w4(qweight: torch.Tensor, to_canonical: bool = False, layout: int = QF_LAYOUT_INTERLEAVED) -> torch.Tensor:
+    """One-time weight permutation: canonical -> `layout` (QF_LAYOUT_INTERLEAVED or QF_LAYOUT_TILED), or back.
+
+    The result has the shape and dtype of the input; only the order of the 4-bit codes changes.
+    """
     dev = _need_cuda(qweight)
     qweight = qweight.contiguous()
+    if layout == QF_LAYOUT_TILED:
+        N = qweight.shape[0]
+        K = qweight.shape[1] * (8 if qweight.dtype == torch.int32 else 2)
+        out = torch.empty_like(qweight)
+        ctx = _ctx(dev)
+        with torch.cuda.device(dev):
+            st = _lib.load().qf_prepack_w4_tiled(ctx, _ptr(qweight), _ptr(out), N, K, 1 if to_canonical else 0,
+                                                 _stream(dev))
+        _check(st, ctx)
+        return out
     nbytes = qweight.numel() * qweight.element_size()
     if nbytes % 4 != 0:
         raise ValueError("qweight must hold whole 32-bit words")
@@ -297,8 +310,8 @@ class W4A16Linear:
         self.group_size, self.zero_const = group_size, zero_const
         self.weight_layout = QF_LAYOUT_CANONICAL
         if prepack and qweight.shape[0] % 128 == 0:
-            self.qweight = prepack_w4(self.qweight)
-            self.weight_layout = QF_LAYOUT_INTERLEAVED
+            self.qweight = prepack_w4(self.qweight, layout=QF_LAYOUT_TILED)
+            self.weight_layout = QF_LAYOUT_TILED
         self.N = qweight.shape[0]
         self.K = qweight.shape[1] * (8 if qweight.dtype == torch.int32 else 2)
 

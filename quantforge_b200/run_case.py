@@ -41,26 +41,66 @@ def main():
     ap.add_argument("--sigma", type=float, default=0.02)
     ap.add_argument("--path", default="auto", choices=["auto", "gemv", "gemm"])
     ap.add_argument("--split-k", type=int, default=0)
+    ap.add_argument("--interleaved", action="store_true", help="prepack the weights (QF_LAYOUT_INTERLEAVED)")
+    ap.add_argument("--tiled", action="store_true", help="prepack the weights (QF_LAYOUT_TILED)")
+    ap.add_argument("--graph", action="store_true",
+                    help="time a CUDA graph of one launch per weight copy instead of single launches")
     args = ap.parse_args()
     dt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
     act = dt[args.act]
     out_dtype = dt[args.out] if args.out else act
     path = {"auto": QF_PATH_AUTO, "gemv": QF_PATH_GEMV, "gemm": QF_PATH_GEMM}[args.path]
     dev = torch.device("cuda:0")
+    if args.graph:
+        args.copies = max(args.copies, -(-300_000_000 // (args.K * args.N // 2)))
     sets = [make_case(args.M, args.K, args.N, act, dev, args.sym, args.sigma, seed=i) for i in range(args.copies)]
+    layout = 0
+    if args.interleaved:
+        sets = [(qf.prepack_w4(qw), sc, zr, x) for (qw, sc, zr, x) in sets]
+        layout = 1
+    if args.tiled:
+        sets = [(qf.prepack_w4(qw, layout=2), sc, zr, x) for (qw, sc, zr, x) in sets]
+        layout = 2
     y = torch.empty(args.M, args.N, dtype=out_dtype, device=dev)
-    times = []
-    for it in range(args.iters + 2):
-        qw, sc, zr, x = sets[it % args.copies]
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
+
+    def launch(i):
+        qw, sc, zr, x = sets[i % args.copies]
         qf.w4a16_linear(x, qw, sc, zr, group_size=128, zero_const=8, out_dtype=out_dtype, path=path,
-                        split_k=args.split_k, out=y)
-        e1.record()
+                        split_k=args.split_k, out=y, weight_layout=layout)
+
+    times = []
+    if args.graph:
+        launch(0)
         torch.cuda.synchronize()
-        if it >= 2:
-            times.append(e0.elapsed_time(e1) * 1e3)
-    print(json.dumps({"M": args.M, "K": args.K, "N": args.N, "act": args.act, "us_min": min(times),
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(args.copies):
+                launch(i)
+        for it in range(args.iters + 2):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            if it >= 2:
+                times.append(e0.elapsed_time(e1) * 1e3 / args.copies)
+    else:
+        for it in range(args.iters + 2):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            launch(it)
+            e1.record()
+            torch.cuda.synchronize()
+            if it >= 2:
+                times.append(e0.elapsed_time(e1) * 1e3)
+    G = args.K // 128
+    out_b = 4 if out_dtype == torch.float32 else 2
+    nbytes = (args.K * args.N // 2 + G * args.N * 2 + (0 if args.sym else G * args.N // 2) + args.M * args.K * 2 +
+              args.M * args.N * out_b)
+    us = min(times)
+    print(json.dumps({"M": args.M, "K": args.K, "N": args.N, "act": args.act, "path": args.path,
+                      "layout": layout, "status": qf.device_status(), "us_min": round(us, 2),
+                      "gbs": round(nbytes / us / 1e3, 1), "tflops": round(2 * args.M * args.K * args.N / us / 1e6, 1),
                       "us_all": [round(t, 2) for t in times]}))
 
 

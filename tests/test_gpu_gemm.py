@@ -9,6 +9,7 @@ pytestmark = pytest.mark.gpu
 
 GEMM = 2  # QF_PATH_GEMM
 INTERLEAVED = 1
+TILED = 2
 _TD = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
 
 
@@ -37,11 +38,13 @@ def _run(qf, M, K, N, g=128, act="bf16", zero_kind="u4", out="f32", seed=0, spli
         z_np, z_t, zc = 8, None, 8
     want = O.w4a16_linear(d["x"], d["qweight"], d["scales"], z_np, g, act, O.F32, accumulate="f64")
     qw = _t(d["qweight"])
-    if interleaved:
+    if interleaved == "tiled":
+        qw = qf.prepack_w4(qw, layout=TILED)
+    elif interleaved:
         qw = qf.prepack_w4(qw)
     y = qf.w4a16_linear(_t(d["x"], _TD[act]), qw, _t(d["scales"], _TD[act]), z_t, group_size=g, zero_const=zc,
                         out_dtype=_TD[out], path=GEMM, split_k=split_k,
-                        weight_layout=INTERLEAVED if interleaved else 0)
+                        weight_layout=TILED if interleaved == "tiled" else INTERLEAVED if interleaved else 0)
     assert qf.device_status() == 0, "a bounded device wait expired"
     return y.float().cpu().numpy(), want
 
@@ -58,15 +61,27 @@ def test_prepack_is_a_permutation_and_round_trips(qf):
     assert np.array_equal(codes_i, codes[:, :, [0, 2, 4, 6, 1, 3, 5, 7]])
 
 
+def test_tiled_prepack_round_trips(qf):
+    rng = np.random.default_rng(1)
+    packed = rng.integers(-128, 128, size=(256, 192), dtype=np.int8)  # N=256, K=384
+    qw = _t(packed)
+    tiled = qf.prepack_w4(qw, layout=TILED)
+    assert tiled.shape == qw.shape and not torch.equal(tiled, qw)
+    assert torch.equal(qf.prepack_w4(tiled, to_canonical=True, layout=TILED), qw)
+    # same multiset of codes: a permutation
+    assert np.array_equal(np.sort(O.unpack_int4(tiled.cpu().numpy()).ravel()), np.sort(O.unpack_int4(packed).ravel()))
+
+
 @pytest.mark.parametrize("M", [16, 1, 9, 17, 32, 33, 64, 100, 128, 200, 256, 300])
-def test_gemm_batch_tiles(qf, M):
-    got, want = _run(qf, M, 512, 256, seed=M)
+@pytest.mark.parametrize("layout", [False, "tiled"])
+def test_gemm_batch_tiles(qf, M, layout):
+    got, want = _run(qf, M, 512, 256, seed=M, interleaved=layout)
     assert O.rel_err(got, want) < 2e-4
 
 
 @pytest.mark.parametrize("act", ["f16", "bf16"])
 @pytest.mark.parametrize("zero_kind", ["u4", "const", "i8"])
-@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("interleaved", [False, True, "tiled"])
 def test_gemm_dtypes_zero_modes_layouts(qf, act, zero_kind, interleaved):
     got, want = _run(qf, 24, 1024, 128, act=act, zero_kind=zero_kind, interleaved=interleaved, seed=3)
     assert O.rel_err(got, want) < 2e-4
@@ -97,13 +112,13 @@ def test_gemm_output_dtypes(qf, out):
 @pytest.mark.parametrize("KN", [(4096, 4096), (4096, 14336), (14336, 4096)])
 def test_gemm_config1_shapes(qf, M, KN):
     K, N = KN
-    got, want = _run(qf, M, K, N, seed=2, interleaved=True)
+    got, want = _run(qf, M, K, N, seed=2, interleaved="tiled")
     assert O.rel_err(got, want) < 1e-2
 
 
 def test_gemm_prefill_slice_symmetric(qf):
     """M=512 rows of the prefill configuration's kind (symmetric zero 8, sigma 0.01, bf16) on a K=8192 slice."""
-    got, want = _run(qf, 512, 8192, 512, zero_kind="const", sigma=0.01, seed=5, interleaved=True)
+    got, want = _run(qf, 512, 8192, 512, zero_kind="const", sigma=0.01, seed=5, interleaved="tiled")
     assert O.rel_err(got, want) < 1e-2
 
 
