@@ -49,8 +49,27 @@ struct GemmCfg {
         STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + STAGES * SZ_BYTES;
 };
 
+// Optional pipeline trace (compile with -DQF_GEMM_TRACE): CTA (0,0,0) writes clock64 stamps per role and k-block.
+#ifdef QF_GEMM_TRACE
+__device__ long long g_qf_trace[4096];
+__device__ long long g_qf_cta[3 * 4096];  // per CTA: globaltimer at start, at end, SM id
+__device__ __forceinline__ long long qf_globaltimer() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define QF_TRACE(role, it, slot)                                                                  \
+    do {                                                                                          \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 64)                   \
+            g_qf_trace[((role) * 64 + (it)) * 8 + (slot)] = clock64();                            \
+    } while (0)
+#else
+#define QF_TRACE(role, it, slot) \
+    do {                         \
+    } while (0)
+#endif
+
 constexpr int GEMM_THREADS = 320;
-constexpr int GEMM_CONV_THREADS = 256;
 
 struct GemmParams {
     const uint16_t *scales;
@@ -169,6 +188,16 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// One lane of a fully active warp (the same lane every time within a kernel).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
 // Arrives on the mbarrier once all MMAs issued so far by this thread have completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -199,15 +228,14 @@ __device__ __forceinline__ int load_zero_rt(const void *zeros, int zmode, int zc
 }
 
 // 4 packed words (32 codes along K) -> 16 registers of 16-bit pairs in natural k order.
-template <bool BF16>
-__device__ __forceinline__ void convert32(const uint4 &v, const ZeroScale<BF16> &zs, bool interleaved,
-                                          uint32_t (&out)[16]) {
+template <bool BF16, bool INTER>
+__device__ __forceinline__ void convert32(const uint4 &v, const ZeroScale<BF16> &zs, uint32_t (&out)[16]) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         uint32_t p[4];
         dequant8<BF16>(w[j], zs, p);  // p[i] = (nibble i, nibble i+4)
-        if (interleaved) {            // nibble order c0 c2 c4 c6 c1 c3 c5 c7: pairs are already (c0,c1)(c2,c3)..
+        if (INTER) {                  // nibble order c0 c2 c4 c6 c1 c3 c5 c7: pairs are already (c0,c1)(c2,c3)..
             out[4 * j + 0] = p[0];
             out[4 * j + 1] = p[1];
             out[4 * j + 2] = p[2];
@@ -224,7 +252,7 @@ __device__ __forceinline__ void convert32(const uint4 &v, const ZeroScale<BF16> 
 // ---------------------------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------------------------
-template <bool BF16, int BN>
+template <bool BF16, int BN, bool INTER>
 __global__ void __launch_bounds__(GEMM_THREADS, GemmCfg<BN>::CTAS_PER_SM)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
             const GemmParams p) {
@@ -261,6 +289,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
     const int64_t n0 = (int64_t)n_tile * 128;
     const int64_t m0 = (int64_t)m_tile * BN;
 
+    if (tid == 0) QF_TRACE(3, 4, 0);
+#ifdef QF_GEMM_TRACE
+    const int cta_lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    if (tid == 0 && cta_lin < 4096) {
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        g_qf_cta[3 * cta_lin] = qf_globaltimer();
+        g_qf_cta[3 * cta_lin + 2] = smid;
+    }
+#endif
     if (tid == 0) {
         s_abort = 0;
         for (int s = 0; s < STAGES; ++s) {
@@ -287,60 +325,95 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
     volatile int *abort_flag = &s_abort;
+    if (tid == 0) QF_TRACE(3, 4, 1);
 
-    int producer_issued = 0;
+    int producer_issued = 0;  // meaningful in the elected producer lane only
     if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
-        if (lane == 0) {
-            for (int it = 0; it < nkb; ++it) {
-                const int s = it % STAGES;
-                const uint32_t ph = (it / STAGES) & 1;
-                if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) break;
+        // The whole warp runs the loop (uniform control flow); one elected lane issues the copies.
+        const bool leader = elect_one();
+        const uint32_t zbytes = p.zero_mode == QF_ZERO_U4 ? 64u : p.zero_mode == QF_ZERO_I8 ? 128u : 0u;
+        const uint32_t tx_bytes = C::STAGE_BYTES + 256u + zbytes;
+        const int group_kb = p.group_size / BK;  // k-blocks per quantisation group (>= 1)
+        int gi = kb0 / group_kb, g_rem = kb0 % group_kb;
+        const uint8_t *sc_ptr = (const uint8_t *)(p.scales + n0) + (size_t)gi * p.N * 2;
+        const size_t z_row = p.zero_mode == QF_ZERO_U4 ? (size_t)p.N / 2 : (size_t)p.N;
+        const uint8_t *z_ptr =
+            (const uint8_t *)p.zeros + (p.zero_mode == QF_ZERO_U4 ? (size_t)n0 / 2 : (size_t)n0) + (size_t)gi * z_row;
+        const int w_row0 = p.tiled ? n_tile * (int)(p.K >> 7) * 128 : (int)n0;
+        int s = 0;
+        uint32_t ph = 0;
+        for (int it = 0; it < nkb; ++it) {
+            QF_TRACE(0, it, 0);
+            const bool ok = mbar_wait(empty_bar(s), ph ^ 1, abort_flag);
+            if (!__all_sync(0xffffffffu, ok)) break;
+            QF_TRACE(0, it, 1);
+            if (leader) {
                 const int kb = kb0 + it;
-                const int64_t gi = ((int64_t)kb * BK) / p.group_size;
-                const uint32_t zbytes = p.zero_mode == QF_ZERO_U4 ? 64u : p.zero_mode == QF_ZERO_I8 ? 128u : 0u;
-                mbar_arrive_expect_tx(full_bar(s), C::STAGE_BYTES + 256u + zbytes);
-                bulk_load(sz_stage(s), p.scales + gi * p.N + n0, 256u, full_bar(s));
-                if (p.zero_mode == QF_ZERO_U4)
-                    bulk_load(sz_stage(s) + 256u, (const uint8_t *)p.zeros + (gi * p.N + n0) / 2, 64u, full_bar(s));
-                else if (p.zero_mode == QF_ZERO_I8)
-                    bulk_load(sz_stage(s) + 256u, (const uint8_t *)p.zeros + gi * p.N + n0, 128u, full_bar(s));
+                const uint32_t fb = full_bar(s);
+                mbar_arrive_expect_tx(fb, tx_bytes);
                 if (p.tiled) {
                     // tile-major weights: rows of 64 bytes, the 128 rows of (n_tile, 128-code block) adjacent
                     const int kb128 = (kb * BK) >> 7;
-                    const int c0 = (BK == 128) ? 0 : (kb & 1) * 32;
-                    tma_load_2d(w_stage(s), &tmap_w, full_bar(s), c0, (n_tile * (int)(p.K >> 7) + kb128) * 128);
+                    tma_load_2d(w_stage(s), &tmap_w, fb, (BK == 128) ? 0 : (kb & 1) * 32, w_row0 + kb128 * 128);
                 } else {
-                    tma_load_2d(w_stage(s), &tmap_w, full_bar(s), kb * C::W_ROW_BYTES, (int)n0);
+                    tma_load_2d(w_stage(s), &tmap_w, fb, kb * C::W_ROW_BYTES, w_row0);
                 }
+                bulk_load(sz_stage(s), sc_ptr, 256u, fb);
+                if (zbytes) bulk_load(sz_stage(s) + 256u, z_ptr, zbytes, fb);
 #pragma unroll
                 for (int b = 0; b < BK / 64; ++b)
-                    tma_load_2d(x_stage(s) + b * C::X_BOX_BYTES, &tmap_x, full_bar(s), kb * BK + b * 64, (int)m0);
+                    tma_load_2d(x_stage(s) + b * C::X_BOX_BYTES, &tmap_x, fb, kb * BK + b * 64, (int)m0);
                 producer_issued = it + 1;
             }
+            if (++g_rem == group_kb) {
+                g_rem = 0;
+                sc_ptr += (size_t)p.N * 2;
+                z_ptr += z_row;
+            }
+            if (++s == STAGES) {
+                s = 0;
+                ph ^= 1;
+            }
+            QF_TRACE(0, it, 2);
         }
     } else if (warp == 9) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
-            const uint32_t idesc = (1u << 4) | ((BF16 ? 1u : 0u) << 7) | ((BF16 ? 1u : 0u) << 10) |
-                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            for (int it = 0; it < nkb; ++it) {
-                const int s = it % STAGES;
-                const uint32_t ph = (it / STAGES) & 1;
-                const int a = it % NA;
-                const uint32_t aph = (it / NA) & 1;
-                if (!mbar_wait(full_bar(s), ph, abort_flag)) break;
-                if (!mbar_wait(afull_bar(a), aph, abort_flag)) break;
-                tc_fence_after();
+        const bool leader = elect_one();
+        const uint32_t idesc = (1u << 4) | ((BF16 ? 1u : 0u) << 7) | ((BF16 ? 1u : 0u) << 10) |
+                               ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        const uint64_t desc_hi = make_b_desc(0) & 0xFFFFFFFF00000000ull;
+        const uint32_t desc_lo_const = (uint32_t)(make_b_desc(0) & 0xFFFFFFFFull);
+        int s = 0, a = 0;
+        uint32_t ph = 0, aph = 0;
+        for (int it = 0; it < nkb; ++it) {
+            QF_TRACE(1, it, 0);
+            bool ok = mbar_wait(full_bar(s), ph, abort_flag);
+            QF_TRACE(1, it, 1);
+            ok = ok && mbar_wait(afull_bar(a), aph, abort_flag);
+            if (!__all_sync(0xffffffffu, ok)) break;
+            QF_TRACE(1, it, 2);
+            tc_fence_after();
+            if (leader) {
                 const uint32_t a_tmem = tmem_base + BN + a * C::A_COLS;
+                const uint32_t lo0 = desc_lo_const | ((x_stage(s) >> 4) & 0x3FFFu);
 #pragma unroll
                 for (int kk = 0; kk < BK / 16; ++kk) {
-                    const uint64_t bdesc = make_b_desc(x_stage(s) + (kk >> 2) * C::X_BOX_BYTES + (kk & 3) * 32);
-                    umma_ts(tmem_base, a_tmem + kk * 8, bdesc, idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                    const uint32_t lo = lo0 + (uint32_t)(((kk >> 2) * C::X_BOX_BYTES + (kk & 3) * 32) >> 4);
+                    umma_ts(tmem_base, a_tmem + kk * 8, desc_hi | lo, idesc, (kk > 0) ? 1u : (it > 0 ? 1u : 0u));
                 }
                 umma_commit(empty_bar(s));
                 umma_commit(aempty_bar(a));
                 if (it == nkb - 1) umma_commit(dfull_bar);
+            }
+            QF_TRACE(1, it, 3);
+            if (++s == STAGES) {
+                s = 0;
+                ph ^= 1;
+            }
+            if (++a == NA) {
+                a = 0;
+                aph ^= 1;
             }
         }
     } else {
@@ -349,7 +422,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
         const int row = tid & 127;             // TMEM lane and weight row inside the tile
         const int64_t n = n0 + row;
         const uint32_t lane_taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-        const bool interleaved = p.interleaved != 0;
         // swizzled 16-byte chunk positions of this row inside a weight stage
         const uint32_t row_off = (uint32_t)row * C::W_ROW_BYTES;
         const uint32_t sw = (BK == 128) ? ((row >> 1) & 3) : ((row >> 2) & 1);
@@ -360,8 +432,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
             const int a = it % NA;
             const uint32_t aph = (it / NA) & 1;
             // warp-uniform outcome: the tcgen05.st below is warp-collective
+            if (row == 0) QF_TRACE(2, it, 0);
             bool ready = mbar_wait(full_bar(s), ph, abort_flag);
+            if (row == 0) QF_TRACE(2, it, 1);
             ready = ready && mbar_wait(aempty_bar(a), aph ^ 1, abort_flag);
+            if (row == 0) QF_TRACE(2, it, 2);
             if (!__all_sync(0xffffffffu, ready)) break;
             tc_fence_after();
             // zero and scale of (this row, this k-block's group) from the stage's slivers
@@ -386,17 +461,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
             for (int c = 0; c < C::W_ROW_BYTES / 16; ++c) {
                 const uint4 v = lds128(wbase + (((uint32_t)c ^ sw) << 4));
                 uint32_t out[16];
-                convert32<BF16>(v, zs, interleaved, out);
+                convert32<BF16, INTER>(v, zs, out);
                 tmem_st16(lane_taddr + a_col + c * 16, out);
             }
+            if (row == 0) QF_TRACE(2, it, 3);
             tmem_wait_st();
+            if (row == 0) QF_TRACE(2, it, 4);
             tc_fence_before();
             mbar_arrive(afull_bar(a));
             mbar_arrive(empty_bar(s));
         }
 
         // ------------------------------ epilogue ------------------------------
+        if (row == 0) QF_TRACE(3, wg, 0);
         const bool ok = __all_sync(0xffffffffu, mbar_wait(dfull_bar, 0, abort_flag));
+        if (row == 0) QF_TRACE(3, wg, 1);
         tc_fence_after();
         if (ok) {
             constexpr int COLS_PER_WG = BN / 2;
@@ -422,17 +501,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
     }
 
     // ------------------------------ teardown ------------------------------
+    if (tid == 0) QF_TRACE(3, 2, 0);
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) QF_TRACE(3, 2, 1);
     if (s_abort) {
-        if (warp == 8 && lane == 0) {
+        if (warp == 8 && producer_issued > 0) {
             // drain this CTA's own TMA copies before the shared memory goes away
             int dummy = 0;
             volatile int *no_abort = &dummy;
             for (int it = max(0, producer_issued - STAGES); it < producer_issued; ++it)
                 mbar_wait(full_bar(it % STAGES), (it / STAGES) & 1, no_abort);
-            atomicExch(p.status, QF_ERR_TIMEOUT);
         }
+        if (tid == 0) atomicExch(p.status, QF_ERR_TIMEOUT);
         __syncthreads();
     } else if (p.split_k > 1) {
         // split-K: last CTA of this (m_tile, n_tile) sums the partial tiles in split order
@@ -464,7 +545,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
     }
+    if (tid == 0) QF_TRACE(3, 3, 0);
+#ifdef QF_GEMM_TRACE
+    if (tid == 0 && cta_lin < 4096) g_qf_cta[3 * cta_lin + 1] = qf_globaltimer();
+#endif
 }
+
+#ifdef QF_GEMM_TRACE
+extern "C" __attribute__((visibility("default"))) int qf_debug_read_trace(long long *host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_qf_trace, sizeof(long long) * 4096);
+}
+extern "C" __attribute__((visibility("default"))) int qf_debug_read_cta(long long *host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_qf_cta, sizeof(long long) * 3 * 4096);
+}
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // host side
@@ -537,7 +631,10 @@ static int get_tensor_map(qf_ctx *ctx, CUtensorMap *out, const void *ptr, int ki
 
 template <bool BF16, int BN>
 static cudaError_t gemm_set_attr() {
-    return cudaFuncSetAttribute(gemm_kernel<BF16, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BF16, BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GemmCfg<BN>::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(gemm_kernel<BF16, BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 GemmCfg<BN>::SMEM_BYTES);
 }
 
@@ -575,7 +672,10 @@ static int gemm_launch_bn(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan
     p.kblocks = (int)(d->K / C::BK);
     p.kblocks_per_split = plan.chunks_per_split;
     dim3 grid((unsigned)plan.m_tiles, (unsigned)(d->N / 128), (unsigned)plan.split_k);
-    gemm_kernel<BF16, BN><<<grid, GEMM_THREADS, C::SMEM_BYTES, s>>>(tw, tx, p);
+    if (p.interleaved)
+        gemm_kernel<BF16, BN, true><<<grid, GEMM_THREADS, C::SMEM_BYTES, s>>>(tw, tx, p);
+    else
+        gemm_kernel<BF16, BN, false><<<grid, GEMM_THREADS, C::SMEM_BYTES, s>>>(tw, tx, p);
     g_launch_count.fetch_add(1);
     QF_CUDA_TRY(ctx, cudaGetLastError());
     return QF_OK;
