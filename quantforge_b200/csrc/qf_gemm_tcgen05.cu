@@ -87,6 +87,7 @@ struct GemmParams {
     int split_k;
     int interleaved;       // weight nibble order inside a word: 0 canonical, 1 pair-interleaved
     int tiled;             // 1: weights stored tile-major (QF_LAYOUT_TILED)
+    const void *qw_raw;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -355,7 +356,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                 if (p.tiled) {
                     // tile-major weights: rows of 64 bytes, the 128 rows of (n_tile, 128-code block) adjacent
                     const int kb128 = (kb * BK) >> 7;
+#ifdef QF_EXP_BULK
+                    bulk_load(w_stage(s), (const uint8_t *)p.qw_raw + (size_t)(w_row0 + kb128 * 128) * 64, 8192u, fb);
+#else
                     tma_load_2d(w_stage(s), &tmap_w, fb, (BK == 128) ? 0 : (kb & 1) * 32, w_row0 + kb128 * 128);
+#endif
                 } else {
                     tma_load_2d(w_stage(s), &tmap_w, fb, kb * C::W_ROW_BYTES, w_row0);
                 }
@@ -398,7 +403,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                 const uint32_t a_tmem = tmem_base + BN + a * C::A_COLS;
                 const uint32_t lo0 = desc_lo_const | ((x_stage(s) >> 4) & 0x3FFFu);
 #pragma unroll
+#ifdef QF_EXP_ONEMMA
+                for (int kk = 0; kk < 1; ++kk) {
+#else
                 for (int kk = 0; kk < BK / 16; ++kk) {
+#endif
                     const uint32_t lo = lo0 + (uint32_t)(((kk >> 2) * C::X_BOX_BYTES + (kk & 3) * 32) >> 4);
                     umma_ts(tmem_base, a_tmem + kk * 8, desc_hi | lo, idesc, (kk > 0) ? 1u : (it > 0 ? 1u : 0u));
                 }
@@ -461,8 +470,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
             for (int c = 0; c < C::W_ROW_BYTES / 16; ++c) {
                 const uint4 v = lds128(wbase + (((uint32_t)c ^ sw) << 4));
                 uint32_t out[16];
+#ifdef QF_EXP_NOCONV
+#pragma unroll
+                for (int q = 0; q < 16; ++q) out[q] = (q & 1) ? v.x : v.y ^ zs.s2;
+#else
                 convert32<BF16, INTER>(v, zs, out);
+#endif
+#ifdef QF_EXP_NOST
+                {
+                    uint32_t acc_x = 0;
+#pragma unroll
+                    for (int q = 0; q < 16; ++q) acc_x ^= out[q];
+                    asm volatile("" ::"r"(acc_x));
+                    if (acc_x == 0x12345678u) tmem_st16(lane_taddr + a_col + c * 16, out);
+                }
+#else
                 tmem_st16(lane_taddr + a_col + c * 16, out);
+#endif
             }
             if (row == 0) QF_TRACE(2, it, 3);
             tmem_wait_st();
@@ -715,6 +739,7 @@ int launch_gemm(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const vo
     p.split_k = plan.split_k;
     p.interleaved = d->weight_layout != QF_LAYOUT_CANONICAL;
     p.tiled = d->weight_layout == QF_LAYOUT_TILED;
+    p.qw_raw = qw;
     if (d->act_dtype == QF_BF16) return gemm_launch_dt<true>(ctx, d, plan, X, qw, p, s);
     return gemm_launch_dt<false>(ctx, d, plan, X, qw, p, s);
 }
