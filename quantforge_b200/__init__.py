@@ -7,6 +7,7 @@ from .ops import (  # noqa: F401
     W4A16Linear, clear_device_status, dequant_w4, device_status, gemv_int4, launch_count, pack_int4, pack_zeros_u4,
     prepack_w4, unpack_int4, w4a16_linear, w4a16_linear_host, workspace_bytes,
 )
-from ._lib import QuantForgeError  # noqa: F401
+from ._lib import (QF_LAYOUT_CANONICAL, QF_LAYOUT_INTERLEAVED, QF_LAYOUT_TILED, QF_PATH_AUTO, QF_PATH_GEMM,  # noqa: F401
+                   QF_PATH_GEMV, QuantForgeError)
 
 __version__ = "0.1.0"
