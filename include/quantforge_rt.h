@@ -156,6 +156,34 @@ int qf_prepack_w4_tiled(qf_ctx *ctx, const void *qweight_in, void *qweight_out, 
 int qf_ctx_status(const qf_ctx *ctx);
 int qf_ctx_clear_status(qf_ctx *ctx);
 
+/*
+ * The GEMV-kernel linear for callers that must not allocate device memory and have no scratch buffer to lend.
+ * (No counterpart in the reference, which has no runtime and therefore no memory policy.)
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits - inside a host framework that owns the whole
+ * device heap and hands plugins raw tensors only, in a latency-critical serving loop where an allocation would
+ * synchronise the device, or in a process started with a fixed memory budget that is already spent on weights.
+ * Such callers cannot provide the split-K `workspace` of qf_w4a16_linear either.
+ *
+ * This entry point runs the same kernel as qf_w4a16_linear with path = QF_PATH_GEMV, but its split-K partial
+ * sums and arrival counters live in a scratch array that is part of the library image: a file-scope
+ * `static __device__` array of QF_STATIC_SCRATCH_BYTES (16 MiB) that every GPU loading the library holds until
+ * the process exits. The call issues no cudaMalloc / cudaFree and calls no allocating library routine.
+ *   - Limits: a linear whose plan needs more scratch than the array holds is refused with QF_ERR_WORKSPACE
+ *     (the message names both sizes); use qf_w4a16_linear with your own workspace for those, or set
+ *     desc.split_k = 1, which needs no scratch at all.
+ *   - The array is shared by every call on that device and keeps the previous call's contents. The counters a
+ *     call uses are cleared on `stream` before the kernel starts; the partial sums are fully overwritten before
+ *     they are read. Two calls that overlap in time on one device (different streams, or different host threads)
+ *     race on the array: serialise them.
+ *   - The first call on each device looks up the array's device address and raises the kernel's shared-memory
+ *     limit. Make that first call outside any stream capture.
+ * `ctx` may be NULL; when given it only receives the error message.
+ */
+#define QF_STATIC_SCRATCH_BYTES (16u << 20)
+int qf_w4a16_gemv_static_scratch(qf_ctx *ctx, const qf_linear_desc *desc, const void *X, const void *qweight,
+                                 const void *scales, const void *qzeros_or_null, void *Y, void *stream);
+
 /* Which kernel family `desc` resolves to (QF_PATH_GEMV / QF_PATH_GEMM) and the K split it will use. */
 int qf_w4a16_plan(const qf_linear_desc *desc, int32_t *path_out, int32_t *split_k_out);
 

@@ -21,7 +21,7 @@ QF_LAYOUT_CANONICAL, QF_LAYOUT_INTERLEAVED, QF_LAYOUT_TILED = 0, 1, 2
 EXPORTS = [
     "qf_version", "qf_status_string", "qf_ctx_create", "qf_ctx_destroy", "qf_last_error", "qf_unpack_int4",
     "qf_dequant_w4", "qf_w4a16_workspace_bytes", "qf_w4a16_linear", "qf_w4a16_linear_host", "qf_w4a16_plan",
-    "qf_launch_count", "qf_prepack_w4", "qf_prepack_w4_tiled", "qf_ctx_status", "qf_ctx_clear_status",
+    "qf_launch_count", "qf_prepack_w4", "qf_prepack_w4_tiled", "qf_w4a16_gemv_static_scratch", "qf_ctx_status", "qf_ctx_clear_status",
 ]
 
 
@@ -69,6 +69,7 @@ def load() -> ctypes.CDLL:
     lib.qf_w4a16_workspace_bytes.argtypes = [dp]
     lib.qf_w4a16_linear.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp, sz, vp]
     lib.qf_w4a16_linear_host.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.qf_w4a16_gemv_static_scratch.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp]
     lib.qf_w4a16_plan.argtypes = [dp, ctypes.POINTER(i32), ctypes.POINTER(i32)]
     lib.qf_launch_count.restype = i64
     lib.qf_prepack_w4.argtypes = [vp, vp, vp, i64, ctypes.c_int, vp]

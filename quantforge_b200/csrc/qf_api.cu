@@ -261,6 +261,26 @@ int qf_w4a16_linear(qf_ctx *ctx, const qf_linear_desc *desc, const void *X, cons
     return launch_gemm(ctx, desc, plan, X, qweight, scales, qzeros_or_null, Y, workspace, (cudaStream_t)stream);
 }
 
+int qf_w4a16_gemv_static_scratch(qf_ctx *ctx, const qf_linear_desc *desc, const void *X, const void *qweight,
+                                 const void *scales, const void *qzeros_or_null, void *Y, void *stream) {
+    if (!desc) return fail(ctx, QF_ERR_BAD_ARG, "desc is null");
+    qf_linear_desc d = *desc;
+    d.path = QF_PATH_GEMV;
+    if (d.weight_layout != QF_LAYOUT_CANONICAL)
+        return fail(ctx, QF_ERR_UNSUPPORTED, "the GEMV kernel reads canonical weights only");
+    Plan plan;
+    std::string why;
+    int st = make_plan(&d, &plan, &why);
+    if (st != QF_OK) return fail(ctx, st, why);
+    if (d.M == 0) return QF_OK;
+    if (!X || !qweight || !scales || !Y) return fail(ctx, QF_ERR_BAD_ARG, "null tensor pointer");
+    if (d.zero_mode != QF_ZERO_CONST && !qzeros_or_null) return fail(ctx, QF_ERR_BAD_ARG, "zero_mode needs a qzeros tensor");
+    if (!aligned16(X) || !aligned16(qweight) || !aligned16(scales) || !aligned16(Y) ||
+        (qzeros_or_null && !aligned16(qzeros_or_null)))
+        return fail(ctx, QF_ERR_BAD_ARG, "device pointers must be 16-byte aligned");
+    return launch_gemv_static(ctx, &d, plan, X, qweight, scales, qzeros_or_null, Y, (cudaStream_t)stream);
+}
+
 static int grow(qf_ctx *ctx, void **buf, size_t *have, size_t need) {
     if (*have >= need) return QF_OK;
     if (*buf) {

@@ -78,6 +78,8 @@ int launch_prepack(qf_ctx *ctx, const void *in, void *out, int64_t n_words, int 
 int launch_prepack_tiled(qf_ctx *ctx, const void *in, void *out, int64_t N, int64_t K, int to_canonical,
                          cudaStream_t s);
 int gemm_block_k(int bn);
+int launch_gemv_static(qf_ctx *ctx, const qf_linear_desc *d, const Plan &p, const void *X, const void *qw,
+                       const void *scales, const void *zeros, void *Y, cudaStream_t s);
 int gemv_init(qf_ctx *ctx);
 int gemm_init(qf_ctx *ctx);
 

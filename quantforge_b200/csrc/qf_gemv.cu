@@ -15,6 +15,8 @@
 // out of the converter as (c_i, c_{i+4}) and the activations are staged ONCE per block into
 // shared memory in that same order; no per-weight shuffle is spent on ordering.
 // Accumulation is fp32 in the MMA accumulators.
+#include <mutex>
+
 #include "qf_common.cuh"
 
 namespace qf {
@@ -292,6 +294,53 @@ int launch_gemv(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const vo
     g_launch_count.fetch_add(1);
     QF_CUDA_TRY(ctx, cudaGetLastError());
     return QF_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Variant for callers that cannot allocate: the split-K scratch is a static device array.
+// ---------------------------------------------------------------------------------------------
+// In host code the name below is only a handle for the symbol, not a device address; the address each
+// device uses is looked up once per device with cudaGetSymbolAddress and cached.
+static __device__ __align__(256) unsigned char g_static_scratch[QF_STATIC_SCRATCH_BYTES];
+
+static std::mutex g_static_mutex;
+static void *g_static_ptr[64] = {nullptr};  // per device ordinal
+
+// Device address of the static scratch on the CURRENT device; first use per device also raises the
+// kernels' dynamic shared-memory limit. Neither step allocates.
+static int static_scratch_for_current_device(qf_ctx *ctx, void **out) {
+    int dev = -1;
+    QF_CUDA_TRY(ctx, cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(ctx, QF_ERR_UNSUPPORTED, "device ordinal out of range");
+    std::lock_guard<std::mutex> g(g_static_mutex);
+    if (!g_static_ptr[dev]) {
+        void *ptr = nullptr;
+        QF_CUDA_TRY(ctx, cudaGetSymbolAddress(&ptr, g_static_scratch));
+        int st = gemv_init(ctx);
+        if (st != QF_OK) return st;
+        g_static_ptr[dev] = ptr;
+    }
+    *out = g_static_ptr[dev];
+    return QF_OK;
+}
+
+int launch_gemv_static(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
+                       const void *scales, const void *zeros, void *Y, cudaStream_t s) {
+    const size_t need = plan.ws_partial_bytes + plan.ws_counter_bytes;
+    if (need > (size_t)QF_STATIC_SCRATCH_BYTES)
+        return fail(ctx, QF_ERR_WORKSPACE,
+                    "this linear needs " + std::to_string(need) + " bytes of split-K scratch but the static array holds " +
+                        std::to_string((size_t)QF_STATIC_SCRATCH_BYTES) +
+                        "; pass split_k = 1 or use qf_w4a16_linear with a caller workspace");
+    void *scratch = nullptr;
+    int st = static_scratch_for_current_device(ctx, &scratch);
+    if (st != QF_OK) return st;
+    if (need > 0) {
+        // the array keeps the previous call's contents: the arrival counters this launch uses must start at zero
+        const size_t n_counters = (size_t)((d->N + GEMV_ROWS_PER_BLOCK - 1) / GEMV_ROWS_PER_BLOCK) * plan.m_tiles;
+        QF_CUDA_TRY(ctx, cudaMemsetAsync(scratch, 0, n_counters * sizeof(int), s));
+    }
+    return launch_gemv(ctx, d, plan, X, qw, scales, zeros, Y, scratch, s);
 }
 
 }  // namespace qf
