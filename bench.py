@@ -228,8 +228,8 @@ def main():
         G = K // GROUP
         for M in SWEEP_MS:
             qw = torch.randint(-128, 128, (Nl, K // 2), dtype=torch.int8, device=dev, generator=gen)
-            # one-time, untimed weight prepack for the linears the tcgen05 kernel serves (M > 8)
-            layout = LAYOUT_INTERLEAVED if (M > 8 and Nl % 128 == 0) else LAYOUT_CANONICAL
+            # one-time, untimed weight prepack for the linears the tcgen05 kernel serves (M > 4)
+            layout = LAYOUT_INTERLEAVED if (M > 4 and Nl % 128 == 0) else LAYOUT_CANONICAL
             if layout != LAYOUT_CANONICAL:
                 qw = qf.prepack_w4(qw, layout=layout)
             sc = (torch.randn(G, Nl, device=dev, generator=gen).abs() * (0.02 / 7.0)).clamp_min(2.0 ** -14).to(
@@ -306,8 +306,8 @@ def main():
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
 
     # ---- roofline of the dominant kernel: the GEMV kernel (M <= 8 cases), timed alone ----
-    gemv_cases = [c for c in cases if c["M"] <= 8]
-    gemm_cases = [c for c in cases if c["M"] > 8]
+    gemv_cases = [c for c in cases if c["M"] <= 4]
+    gemm_cases = [c for c in cases if c["M"] > 4]
     roof = {}
     for name, sub in (("gemv", gemv_cases), ("gemm", gemm_cases)):
         # two different shape orders per replay so consecutive launches never share weights
@@ -321,7 +321,7 @@ def main():
                 "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": roof[dom]["achieved"] / pk["hbm_gbs"],
                 "traffic": None, "peak_source": pk["source"], "avg_launch_us": roof[dom]["avg_us"],
                 "algorithmic_bytes_per_launch": roof[dom]["bytes_per_launch"],
-                "other_kernels": {"gemm_m16_m64": {"achieved": roof["gemm"]["achieved"],
+                "other_kernels": {"gemm_m8_m16_m64": {"achieved": roof["gemm"]["achieved"],
                                                    "frac": roof["gemm"]["achieved"] / pk["hbm_gbs"],
                                                    "avg_launch_us": roof["gemm"]["avg_us"]}}}
 
@@ -359,7 +359,7 @@ def main():
         wbytes = K * N // 2
         n = copies or max(3, -(-300_000_000 // wbytes))
         G = K // GROUP
-        layout = LAYOUT_INTERLEAVED if (M > 8 and N % 128 == 0) else LAYOUT_CANONICAL
+        layout = LAYOUT_INTERLEAVED if (M > 4 and N % 128 == 0) else LAYOUT_CANONICAL
         sets = []
         for _ in range(n):
             qw = torch.randint(-128, 128, (N, K // 2), dtype=torch.int8, device=dev, generator=gen)

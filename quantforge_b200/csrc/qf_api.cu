@@ -43,7 +43,7 @@ int make_plan(const qf_linear_desc *d, Plan *p, std::string *why) {
         if (d->reserved[i] != 0) return bad(QF_ERR_BAD_ARG, "reserved fields must be zero");
 
     int path = d->path;
-    if (path == QF_PATH_AUTO) path = (d->M <= 8) ? QF_PATH_GEMV : QF_PATH_GEMM;
+    if (path == QF_PATH_AUTO) path = (d->M <= 4) ? QF_PATH_GEMV : QF_PATH_GEMM;
     if (path != QF_PATH_GEMV && path != QF_PATH_GEMM) return bad(QF_ERR_BAD_ARG, "unknown path");
     if (path == QF_PATH_GEMM && d->N % 128 != 0) {
         if (d->path == QF_PATH_GEMM) return bad(QF_ERR_BAD_ARG, "the GEMM path needs N to be a multiple of 128");
@@ -73,11 +73,11 @@ int make_plan(const qf_linear_desc *d, Plan *p, std::string *why) {
         }
         if (split > chunks) split = chunks;
         int cps = (chunks + split - 1) / split;
-        if (cps > 48) cps = 48;
+        if (cps > 32) cps = 32;
         split = (chunks + cps - 1) / cps;
         p->split_k = split;
         p->chunks_per_split = cps;
-        if (col_blocks * p->m_tiles > kMaxCounters) split = 1, cps = chunks > 48 ? 48 : chunks;
+        if (col_blocks * p->m_tiles > kMaxCounters) split = 1, cps = chunks > 32 ? 32 : chunks;
         if (cps * split < chunks) return bad(QF_ERR_UNSUPPORTED, "K too large for this N on the GEMV path");
         p->split_k = split;
         p->chunks_per_split = cps;

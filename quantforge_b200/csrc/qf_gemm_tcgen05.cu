@@ -49,26 +49,6 @@ struct GemmCfg {
         STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + STAGES * SZ_BYTES;
 };
 
-// Optional pipeline trace (compile with -DQF_GEMM_TRACE): CTA (0,0,0) writes clock64 stamps per role and k-block.
-#ifdef QF_GEMM_TRACE
-__device__ long long g_qf_trace[4096];
-__device__ long long g_qf_cta[3 * 4096];  // per CTA: globaltimer at start, at end, SM id
-__device__ __forceinline__ long long qf_globaltimer() {
-    long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define QF_TRACE(role, it, slot)                                                                  \
-    do {                                                                                          \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 64)                   \
-            g_qf_trace[((role) * 64 + (it)) * 8 + (slot)] = clock64();                            \
-    } while (0)
-#else
-#define QF_TRACE(role, it, slot) \
-    do {                         \
-    } while (0)
-#endif
-
 constexpr int GEMM_THREADS = 320;
 
 struct GemmParams {
@@ -87,7 +67,6 @@ struct GemmParams {
     int split_k;
     int interleaved;       // weight nibble order inside a word: 0 canonical, 1 pair-interleaved
     int tiled;             // 1: weights stored tile-major (QF_LAYOUT_TILED)
-    const void *qw_raw;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -290,16 +269,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
     const int64_t n0 = (int64_t)n_tile * 128;
     const int64_t m0 = (int64_t)m_tile * BN;
 
-    if (tid == 0) QF_TRACE(3, 4, 0);
-#ifdef QF_GEMM_TRACE
-    const int cta_lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-    if (tid == 0 && cta_lin < 4096) {
-        uint32_t smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        g_qf_cta[3 * cta_lin] = qf_globaltimer();
-        g_qf_cta[3 * cta_lin + 2] = smid;
-    }
-#endif
     if (tid == 0) {
         s_abort = 0;
         for (int s = 0; s < STAGES; ++s) {
@@ -326,7 +295,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
     volatile int *abort_flag = &s_abort;
-    if (tid == 0) QF_TRACE(3, 4, 1);
 
     int producer_issued = 0;  // meaningful in the elected producer lane only
     if (warp == 8) {
@@ -345,10 +313,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
         int s = 0;
         uint32_t ph = 0;
         for (int it = 0; it < nkb; ++it) {
-            QF_TRACE(0, it, 0);
             const bool ok = mbar_wait(empty_bar(s), ph ^ 1, abort_flag);
             if (!__all_sync(0xffffffffu, ok)) break;
-            QF_TRACE(0, it, 1);
             if (leader) {
                 const int kb = kb0 + it;
                 const uint32_t fb = full_bar(s);
@@ -356,11 +322,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                 if (p.tiled) {
                     // tile-major weights: rows of 64 bytes, the 128 rows of (n_tile, 128-code block) adjacent
                     const int kb128 = (kb * BK) >> 7;
-#ifdef QF_EXP_BULK
-                    bulk_load(w_stage(s), (const uint8_t *)p.qw_raw + (size_t)(w_row0 + kb128 * 128) * 64, 8192u, fb);
-#else
                     tma_load_2d(w_stage(s), &tmap_w, fb, (BK == 128) ? 0 : (kb & 1) * 32, w_row0 + kb128 * 128);
-#endif
                 } else {
                     tma_load_2d(w_stage(s), &tmap_w, fb, kb * C::W_ROW_BYTES, w_row0);
                 }
@@ -380,7 +342,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                 s = 0;
                 ph ^= 1;
             }
-            QF_TRACE(0, it, 2);
         }
     } else if (warp == 9) {
         // ------------------------------ MMA issuer ------------------------------
@@ -392,22 +353,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
         int s = 0, a = 0;
         uint32_t ph = 0, aph = 0;
         for (int it = 0; it < nkb; ++it) {
-            QF_TRACE(1, it, 0);
             bool ok = mbar_wait(full_bar(s), ph, abort_flag);
-            QF_TRACE(1, it, 1);
             ok = ok && mbar_wait(afull_bar(a), aph, abort_flag);
             if (!__all_sync(0xffffffffu, ok)) break;
-            QF_TRACE(1, it, 2);
             tc_fence_after();
             if (leader) {
                 const uint32_t a_tmem = tmem_base + BN + a * C::A_COLS;
                 const uint32_t lo0 = desc_lo_const | ((x_stage(s) >> 4) & 0x3FFFu);
 #pragma unroll
-#ifdef QF_EXP_ONEMMA
-                for (int kk = 0; kk < 1; ++kk) {
-#else
                 for (int kk = 0; kk < BK / 16; ++kk) {
-#endif
                     const uint32_t lo = lo0 + (uint32_t)(((kk >> 2) * C::X_BOX_BYTES + (kk & 3) * 32) >> 4);
                     umma_ts(tmem_base, a_tmem + kk * 8, desc_hi | lo, idesc, (kk > 0) ? 1u : (it > 0 ? 1u : 0u));
                 }
@@ -415,7 +369,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                 umma_commit(aempty_bar(a));
                 if (it == nkb - 1) umma_commit(dfull_bar);
             }
-            QF_TRACE(1, it, 3);
             if (++s == STAGES) {
                 s = 0;
                 ph ^= 1;
@@ -441,11 +394,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
             const int a = it % NA;
             const uint32_t aph = (it / NA) & 1;
             // warp-uniform outcome: the tcgen05.st below is warp-collective
-            if (row == 0) QF_TRACE(2, it, 0);
             bool ready = mbar_wait(full_bar(s), ph, abort_flag);
-            if (row == 0) QF_TRACE(2, it, 1);
             ready = ready && mbar_wait(aempty_bar(a), aph ^ 1, abort_flag);
-            if (row == 0) QF_TRACE(2, it, 2);
             if (!__all_sync(0xffffffffu, ready)) break;
             tc_fence_after();
             // zero and scale of (this row, this k-block's group) from the stage's slivers
@@ -470,36 +420,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
             for (int c = 0; c < C::W_ROW_BYTES / 16; ++c) {
                 const uint4 v = lds128(wbase + (((uint32_t)c ^ sw) << 4));
                 uint32_t out[16];
-#ifdef QF_EXP_NOCONV
-#pragma unroll
-                for (int q = 0; q < 16; ++q) out[q] = (q & 1) ? v.x : v.y ^ zs.s2;
-#else
                 convert32<BF16, INTER>(v, zs, out);
-#endif
-#ifdef QF_EXP_NOST
-                {
-                    uint32_t acc_x = 0;
-#pragma unroll
-                    for (int q = 0; q < 16; ++q) acc_x ^= out[q];
-                    asm volatile("" ::"r"(acc_x));
-                    if (acc_x == 0x12345678u) tmem_st16(lane_taddr + a_col + c * 16, out);
-                }
-#else
                 tmem_st16(lane_taddr + a_col + c * 16, out);
-#endif
             }
-            if (row == 0) QF_TRACE(2, it, 3);
             tmem_wait_st();
-            if (row == 0) QF_TRACE(2, it, 4);
             tc_fence_before();
             mbar_arrive(afull_bar(a));
             mbar_arrive(empty_bar(s));
         }
 
         // ------------------------------ epilogue ------------------------------
-        if (row == 0) QF_TRACE(3, wg, 0);
         const bool ok = __all_sync(0xffffffffu, mbar_wait(dfull_bar, 0, abort_flag));
-        if (row == 0) QF_TRACE(3, wg, 1);
         tc_fence_after();
         if (ok) {
             constexpr int COLS_PER_WG = BN / 2;
@@ -525,10 +456,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
     }
 
     // ------------------------------ teardown ------------------------------
-    if (tid == 0) QF_TRACE(3, 2, 0);
     tc_fence_before();
     __syncthreads();
-    if (tid == 0) QF_TRACE(3, 2, 1);
     if (s_abort) {
         if (warp == 8 && producer_issued > 0) {
             // drain this CTA's own TMA copies before the shared memory goes away
@@ -569,20 +498,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
     }
-    if (tid == 0) QF_TRACE(3, 3, 0);
-#ifdef QF_GEMM_TRACE
-    if (tid == 0 && cta_lin < 4096) g_qf_cta[3 * cta_lin + 1] = qf_globaltimer();
-#endif
 }
 
-#ifdef QF_GEMM_TRACE
-extern "C" __attribute__((visibility("default"))) int qf_debug_read_trace(long long *host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_qf_trace, sizeof(long long) * 4096);
-}
-extern "C" __attribute__((visibility("default"))) int qf_debug_read_cta(long long *host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_qf_cta, sizeof(long long) * 3 * 4096);
-}
-#endif
 
 // ---------------------------------------------------------------------------------------------
 // host side
@@ -739,7 +656,6 @@ int launch_gemm(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const vo
     p.split_k = plan.split_k;
     p.interleaved = d->weight_layout != QF_LAYOUT_CANONICAL;
     p.tiled = d->weight_layout == QF_LAYOUT_TILED;
-    p.qw_raw = qw;
     if (d->act_dtype == QF_BF16) return gemm_launch_dt<true>(ctx, d, plan, X, qw, p, s);
     return gemm_launch_dt<false>(ctx, d, plan, X, qw, p, s);
 }

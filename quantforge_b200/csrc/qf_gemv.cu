@@ -7,14 +7,17 @@
 //   grid.y : K splits (split-K); partial sums meet in caller-provided fp32 scratch, the last
 //            block to arrive for a column block sums them in split order (deterministic)
 //   grid.z : batch tiles of 8 rows of X
-// Per warp and 128-code chunk of K: every lane loads 16 B (32 codes) of weight row g = lane/4
-// and of row g+8 with 128-bit loads that bypass L1 (the 4 lanes of a row cover 64 contiguous
-// bytes), converts them with lop3 / packed-half arithmetic (zero and scale applied in registers)
-// into the A fragments of eight m16n8k16 tensor-core MMAs, whose B fragments are the activations.
-// The contraction index may be permuted freely as long as A and B agree, so the code pairs come
-// out of the converter as (c_i, c_{i+4}) and the activations are staged ONCE per block into
-// shared memory in that same order; no per-weight shuffle is spent on ordering.
-// Accumulation is fp32 in the MMA accumulators.
+// Weight stream: every lane copies 16 B (32 codes) of weight row g = lane/4 and of row g+8 per
+// 128-code chunk of K with cp.async.cg (L2 -> shared memory, no registers, no L1) into a ring that is
+// PRIVATE to the lane, GEMV_DEPTH chunks deep; a lane reads back only what it copied itself, so the
+// stream needs no block-level synchronisation. The 4 lanes of a row cover 64 contiguous bytes and
+// the ring keeps 512 contiguous bytes per row in flight.
+// Per block, once: the (row, group) constants of the converter (magic+zero, duplicated scale) are
+// computed into a shared table, and the activations are staged in the order the converter produces
+// code pairs, (c_i, c_{i+4}) -- the contraction index may be permuted freely as long as A and B
+// agree -- so no per-weight shuffle is spent on ordering.
+// Per warp and chunk: 2 x 16 B of codes -> lop3 / packed 16-bit arithmetic -> A fragments of eight
+// m16n8k16 tensor-core MMAs whose B fragments are the staged activations; fp32 accumulation.
 #include <mutex>
 
 #include "qf_common.cuh"
@@ -24,8 +27,9 @@ namespace qf {
 constexpr int GEMV_THREADS = 128;
 constexpr int GEMV_WARPS = 4;
 constexpr int GEMV_ROWS_PER_BLOCK = 16 * GEMV_WARPS;  // 64
-constexpr int GEMV_CB = 4;                            // chunks (of 128 codes) per register batch
-constexpr int GEMV_MAX_CHUNKS_PER_SPLIT = 48;         // 2 KB of staged activations per chunk
+constexpr int GEMV_DEPTH = 8;                         // chunks in flight per lane
+constexpr int GEMV_MAX_CHUNKS_PER_SPLIT = 32;
+constexpr int GEMV_RING_BYTES = GEMV_DEPTH * 2 * GEMV_THREADS * 16;  // 32 KB
 
 struct GemvParams {
     const uint16_t *X;
@@ -42,7 +46,14 @@ struct GemvParams {
     int split_k;
     int out_dtype;
     int zero_const;
+    int m_pad;          // rows of X staged per batch tile: 1, 2, 4 or 8
 };
+
+// dynamic shared memory: ring | constants table [chunks][64 rows] uint2 | staged X [chunks][4][m_pad][4] uint4
+static inline size_t gemv_smem_bytes(int chunks_per_split, int m_pad) {
+    return (size_t)GEMV_RING_BYTES + (size_t)chunks_per_split * GEMV_ROWS_PER_BLOCK * 8 +
+           (size_t)chunks_per_split * 4 * m_pad * 4 * 16;
+}
 
 template <bool BF16>
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -60,78 +71,39 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
     }
 }
 
-__device__ __forceinline__ uint4 ldg_stream(const void *p) {
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint4 lds128g(uint32_t addr) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64g(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
     return v;
 }
 
-// One register batch: weights of rows g / g+8 for up to GEMV_CB chunks plus their scales and zeros.
-struct WBatch {
-    uint4 wa[GEMV_CB], wb[GEMV_CB];
-    uint32_t sc[GEMV_CB];  // scale(row g) | scale(row g+8) << 16
-    int z[GEMV_CB];        // zero(row g) & 0xffff | zero(row g+8) << 16  (signed 16-bit fields)
-};
-
-template <int ZMODE>
-__device__ __forceinline__ void load_batch(WBatch &b, const GemvParams &p, int64_t row_a, int c_begin, int c_end,
-                                           int t) {
-    const int64_t words_per_row = p.K >> 3;
-    const uint32_t *ra = p.qw + row_a * words_per_row + t * 4;
-    const uint32_t *rb = ra + 8 * words_per_row;
-#pragma unroll
-    for (int i = 0; i < GEMV_CB; ++i) {
-        const int c = c_begin + i;
-        if (c < c_end) {
-            b.wa[i] = ldg_stream(ra + (int64_t)c * 16);
-            b.wb[i] = ldg_stream(rb + (int64_t)c * 16);
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < GEMV_CB; ++i) {
-        const int c = c_begin + i;
-        if (c < c_end) {
-            const int64_t gi = c / p.group_chunks;
-            const uint32_t sa = __ldg(p.scales + gi * p.N + row_a);
-            const uint32_t sb = __ldg(p.scales + gi * p.N + row_a + 8);
-            b.sc[i] = sa | (sb << 16);
-            const int za = load_zero<ZMODE>(p.zeros, p.zero_const, gi, row_a, p.N);
-            const int zb = load_zero<ZMODE>(p.zeros, p.zero_const, gi, row_a + 8, p.N);
-            b.z[i] = (za & 0xffff) | (zb << 16);
-        }
-    }
-}
-
+// Converter constants from a table entry (x = magic+zero duplicated, y = scale duplicated).
 template <bool BF16>
-__device__ __forceinline__ void compute_batch(const WBatch &b, float (&acc)[2][4], const uint4 *xs, int c_local_begin,
-                                              int n_valid, int lane) {
-#pragma unroll
-    for (int i = 0; i < GEMV_CB; ++i) {
-        if (i < n_valid) {
-            ZeroScale<BF16> za, zb;
-            za.set((int)(short)(b.z[i] & 0xffff), b.sc[i] & 0xffffu);
-            zb.set(b.z[i] >> 16, b.sc[i] >> 16);
-            const uint32_t wa[4] = {b.wa[i].x, b.wa[i].y, b.wa[i].z, b.wa[i].w};
-            const uint32_t wb[4] = {b.wb[i].x, b.wb[i].y, b.wb[i].z, b.wb[i].w};
-            const uint4 *xc = xs + (size_t)(c_local_begin + i) * 128 + lane;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint32_t pa[4], pb[4];
-                dequant8<BF16>(wa[j], za, pa);
-                dequant8<BF16>(wb[j], zb, pb);
-                const uint4 xb = xc[j * 32];
-                mma_16816<BF16>(acc[0], pa[0], pb[0], pa[1], pb[1], xb.x, xb.y);
-                mma_16816<BF16>(acc[1], pa[2], pb[2], pa[3], pb[3], xb.z, xb.w);
-            }
-        }
-    }
+__device__ __forceinline__ ZeroScale<BF16> consts_from(const uint2 e) {
+    ZeroScale<BF16> zs;
+    zs.zsub = e.x;
+    zs.s2 = e.y;
+    // f16 only: -(64 + z) = (1024 + z) * (-1) + 960, exact in f16
+    zs.zfma = BF16 ? 0u : fma_f16x2(e.x, 0xbc00bc00u, 0x63806380u);
+    return zs;
 }
 
 template <bool BF16, int ZMODE>
-__global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) {
-    extern __shared__ uint4 xs[];  // [chunk_local][j][m 0..7][t 0..3]
+__global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
     __shared__ int s_is_last;
 
     const int tid = threadIdx.x;
@@ -143,22 +115,51 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
     const int mt = blockIdx.z;
     const int c0 = split * p.chunks_per_split;
     const int c1 = min(c0 + p.chunks_per_split, p.chunks);
+    const int nch = c1 - c0;
     const int64_t n_blk = (int64_t)blockIdx.x * GEMV_ROWS_PER_BLOCK;
     const int64_t row_a = n_blk + warp * 16 + g;
     const bool warp_active = (n_blk + warp * 16) < p.N;  // N is a multiple of 16
+    const int m_pad = p.m_pad;
 
-    // 1. first weight batch in flight before anything else
-    WBatch A, B;
-    if (warp_active) load_batch<ZMODE>(A, p, row_a, c0, c1, t);
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem_raw) + (uint32_t)tid * 16u;  // + slot * 2048
+    const uint32_t table = (uint32_t)__cvta_generic_to_shared(smem_raw) + GEMV_RING_BYTES;     // [chunk][64] uint2
+    const uint32_t xs = table + (uint32_t)p.chunks_per_split * GEMV_ROWS_PER_BLOCK * 8u;       // [chunk][4][m_pad][4]
 
-    // 2. stage the activations of this K range in fragment order, zero rows beyond M
+    // 1. weight stream: fill the ring before anything else
+    const uint32_t *ra = p.qw + row_a * (p.K >> 3) + (int64_t)c0 * 16 + t * 4;
+    const uint32_t *rb = ra + 8 * (p.K >> 3);
+#pragma unroll
+    for (int i = 0; i < GEMV_DEPTH; ++i) {
+        if (warp_active && i < nch) {
+            cp_async16(ring + (uint32_t)(2 * i) * 2048u, ra + i * 16);
+            cp_async16(ring + (uint32_t)(2 * i + 1) * 2048u, rb + i * 16);
+        }
+        cp_async_commit();
+    }
+
+    // 2. converter constants of this block's (chunk, row) pairs
+    for (int e = tid; e < nch * GEMV_ROWS_PER_BLOCK; e += GEMV_THREADS) {
+        const int r = e & (GEMV_ROWS_PER_BLOCK - 1);
+        const int cl = e >> 6;
+        const int64_t n = n_blk + r;
+        uint2 ent = make_uint2(0u, 0u);
+        if (n < p.N) {
+            const int64_t gi = (c0 + cl) / p.group_chunks;
+            ZeroScale<BF16> zs;
+            zs.set(load_zero<ZMODE>(p.zeros, p.zero_const, gi, n, p.N), __ldg(p.scales + gi * p.N + n));
+            ent = make_uint2(zs.zsub, zs.s2);
+        }
+        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(table + (uint32_t)e * 8u), "r"(ent.x), "r"(ent.y));
+    }
+
+    // 3. activations of this K range in fragment order, zero rows beyond M
     {
-        const int n_units = (c1 - c0) * 128;  // uint4 units: chunk x (m 8) x (16 B pieces 16)
+        const int units_per_chunk = m_pad * 16;  // 16-byte pieces: (m) x (t*4 + j)
         const int64_t m_base = (int64_t)mt * 8;
-        for (int u = tid; u < n_units; u += GEMV_THREADS) {
+        for (int u = tid; u < nch * units_per_chunk; u += GEMV_THREADS) {
             const int piece = u & 15;  // = t*4 + j : 16-byte piece of the chunk's 256-byte row segment
-            const int m = (u >> 4) & 7;
-            const int cl = u >> 7;
+            const int m = (u >> 4) % m_pad;
+            const int cl = u / units_per_chunk;
             uint4 r = make_uint4(0u, 0u, 0u, 0u);
             if (m_base + m < p.M) {
                 const uint4 v = *reinterpret_cast<const uint4 *>(p.X + (m_base + m) * p.K + (int64_t)(c0 + cl) * 128 +
@@ -169,26 +170,49 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
                 r.w = prmt(v.y, v.w, 0x7632u);  // (e3, e7)
             }
             const int tt = piece >> 2, j = piece & 3;
-            xs[((cl * 4 + j) * 8 + m) * 4 + tt] = r;
+            const uint32_t dst = xs + (uint32_t)((((cl * 4 + j) * m_pad + m) * 4 + tt) * 16);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(r.x), "r"(r.y), "r"(r.z), "r"(r.w));
         }
     }
     __syncthreads();
 
-    // 3. main loop, register double buffering
+    // 4. main loop: wait for the oldest chunk of the ring, read it back, refill its slot, convert, MMA
     float acc2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // two chains: MMAs of one chain are dependent
     if (warp_active) {
-        for (int c = c0; c < c1; c += 2 * GEMV_CB) {
-            const bool has_b = (c + GEMV_CB) < c1;
-            if (has_b) load_batch<ZMODE>(B, p, row_a, c + GEMV_CB, c1, t);
-            compute_batch<BF16>(A, acc2, xs, c - c0, min(GEMV_CB, c1 - c), lane);
-            if (has_b) {
-                if (c + 2 * GEMV_CB < c1) load_batch<ZMODE>(A, p, row_a, c + 2 * GEMV_CB, c1, t);
-                compute_batch<BF16>(B, acc2, xs, c + GEMV_CB - c0, min(GEMV_CB, c1 - c - GEMV_CB), lane);
+        // Batch columns >= m_pad of the MMA are never stored, so their lanes may read any staged row:
+        // wrap g into the staged rows instead of zero-filling registers.
+        const uint32_t x_lane = xs + (uint32_t)(((g & (m_pad - 1)) * 4 + t) * 16);
+        const uint32_t tab_a = table + (uint32_t)(warp * 16 + g) * 8u;
+        for (int i = 0; i < nch; ++i) {
+            cp_async_wait<GEMV_DEPTH - 1>();
+            const int slot = i & (GEMV_DEPTH - 1);
+            const uint4 va = lds128g(ring + (uint32_t)(2 * slot) * 2048u);
+            const uint4 vb = lds128g(ring + (uint32_t)(2 * slot + 1) * 2048u);
+            if (i + GEMV_DEPTH < nch) {
+                cp_async16(ring + (uint32_t)(2 * slot) * 2048u, ra + (i + GEMV_DEPTH) * 16);
+                cp_async16(ring + (uint32_t)(2 * slot + 1) * 2048u, rb + (i + GEMV_DEPTH) * 16);
+            }
+            cp_async_commit();
+            const ZeroScale<BF16> za = consts_from<BF16>(lds64g(tab_a + (uint32_t)i * (GEMV_ROWS_PER_BLOCK * 8u)));
+            const ZeroScale<BF16> zb =
+                consts_from<BF16>(lds64g(tab_a + (uint32_t)i * (GEMV_ROWS_PER_BLOCK * 8u) + 64u));
+            const uint32_t wa[4] = {va.x, va.y, va.z, va.w};
+            const uint32_t wb[4] = {vb.x, vb.y, vb.z, vb.w};
+            const uint32_t xc = x_lane + (uint32_t)(i * 4 * m_pad * 64);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t pa[4], pb[4];
+                dequant8<BF16>(wa[j], za, pa);
+                dequant8<BF16>(wb[j], zb, pb);
+                const uint4 xb = lds128g(xc + (uint32_t)(j * m_pad * 64));
+                mma_16816<BF16>(acc2[0], pa[0], pb[0], pa[1], pb[1], xb.x, xb.y);
+                mma_16816<BF16>(acc2[1], pa[2], pb[2], pa[3], pb[3], xb.z, xb.w);
             }
         }
     }
+    cp_async_wait<0>();
 
-    // 4. epilogue. acc[0..1]: row g, batch 2t, 2t+1 ; acc[2..3]: row g+8
+    // 5. epilogue. acc[0..1]: row g, batch 2t, 2t+1 ; acc[2..3]: row g+8
     float acc[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[i] = acc2[0][i] + acc2[1][i];
@@ -207,7 +231,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
     }
 
     const int64_t Mp = (int64_t)gridDim.z * 8;
-    if (warp_active) {
+    if (warp_active && 2 * t < m_pad) {
         float *dst = p.partial + ((int64_t)split * Mp + m0) * p.N;
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
@@ -226,7 +250,8 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
     __syncthreads();
     if (!s_is_last) return;
     __threadfence();
-    for (int u = tid; u < GEMV_ROWS_PER_BLOCK * 8; u += GEMV_THREADS) {
+    const int m_rows = min(8, m_pad + (m_pad & 1));  // rows of this batch tile that hold partial sums
+    for (int u = tid; u < GEMV_ROWS_PER_BLOCK * m_rows; u += GEMV_THREADS) {
         const int nl = u & (GEMV_ROWS_PER_BLOCK - 1);
         const int m = u / GEMV_ROWS_PER_BLOCK;
         const int64_t n = n_blk + nl;
@@ -242,7 +267,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
 template <bool BF16, int ZMODE>
 static cudaError_t set_attr() {
     return cudaFuncSetAttribute(gemv_kernel<BF16, ZMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                GEMV_MAX_CHUNKS_PER_SPLIT * 2048);
+                                (int)gemv_smem_bytes(GEMV_MAX_CHUNKS_PER_SPLIT, 8));
 }
 
 int gemv_init(qf_ctx *ctx) {
@@ -286,7 +311,9 @@ int launch_gemv(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const vo
     p.zero_const = d->zero_const;
     dim3 grid((unsigned)((d->N + GEMV_ROWS_PER_BLOCK - 1) / GEMV_ROWS_PER_BLOCK), (unsigned)plan.split_k,
               (unsigned)plan.m_tiles);
-    const size_t smem = (size_t)plan.chunks_per_split * 2048;
+    const int64_t m_in_tile = d->M < 8 ? d->M : 8;
+    p.m_pad = m_in_tile <= 1 ? 1 : m_in_tile <= 2 ? 2 : m_in_tile <= 4 ? 4 : 8;
+    const size_t smem = gemv_smem_bytes(plan.chunks_per_split, p.m_pad);
     if (d->act_dtype == QF_BF16)
         gemv_dispatch<true>(d->zero_mode, grid, smem, s, p);
     else
