@@ -96,6 +96,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 
 // Bounded wait (about half a second of SM clocks). Returns false on expiry or when another role aborted.
+// A waiting warp backs off with nanosleep so that its polling does not take issue slots from the warps
+// that convert; the sleep is short next to the time a pipeline step takes.
 constexpr long long kWaitCycles = 1000000000LL;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -103,6 +105,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     int it = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(it < 8 ? 20 : 60);
         if ((++it & 63) == 0) {
             if (*abort_flag) return false;
             if (clock64() - t0 > kWaitCycles) {
