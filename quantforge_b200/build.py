@@ -69,5 +69,19 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+OPT_SRC = os.path.join(HERE, "opt", "quantforge_opt.cpp")
+OPT_BIN = os.path.join(HERE, "bin", "quantforge-opt")
+
+
+def build_opt(force: bool = False) -> str:
+    """Builds the re-hosted quantforge-opt driver (plain C++17, no MLIR dependency)."""
+    if not force and os.path.exists(OPT_BIN) and os.path.getmtime(OPT_BIN) >= os.path.getmtime(OPT_SRC):
+        return OPT_BIN
+    os.makedirs(os.path.dirname(OPT_BIN), exist_ok=True)
+    subprocess.run(["g++", "-O2", "-std=c++17", "-Wall", "-o", OPT_BIN, OPT_SRC], check=True)
+    return OPT_BIN
+
+
 if __name__ == "__main__":
+    print(build_opt(force="--force" in sys.argv))
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
