@@ -182,6 +182,67 @@ def run_reference_arm(args):
 
 
 # ------------------------------------------------------------------------------------------------
+# decode-linear stack workloads (Llama-3-8B / 70B shaped layers, tensor parallel over the ranks)
+# ------------------------------------------------------------------------------------------------
+def time_stack(stack, torch, dist, dev, world, steps, warmup):
+    g = stack.capture()
+    for _ in range(warmup):
+        g.replay()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        g.replay()
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / steps, g
+
+
+def run_stack_workload(args, qf, torch, dist, dev, world, rank, local_rank, pk):
+    from quantforge_b200 import stack as S
+    cfg = S.LLAMA3_8B if args.workload == "stack8b" else S.LLAMA3_70B
+    st = S.DecodeLinearStack(cfg, args.batch, torch.bfloat16, dev, world, rank, None, args.layers or None)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, g = time_stack(st, torch, dist, dev, world, args.steps, args.warmup)
+    t_end = time.time() + 1.5
+    while time.time() < t_end:
+        for _ in range(5):
+            g.replay()
+        torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    nbytes = st.bytes_per_step()
+    if rank == 0:
+        us = ms * 1e3
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        line = {
+            "metric": "decode_linear_us_per_token", "value": us, "unit": "us", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "batch": args.batch, "layers": st.L, "group_size": GROUP,
+                       "parallelism": "single GPU" if world == 1 else
+                       f"tensor parallel x{world}: column q/k/v/gate/up, row o/down + NCCL all-reduce (bf16)",
+                       "l2": f"weights of the step: {nbytes / 1e9:.2f} GB, far above L2",
+                       "timing": "CUDA graph of one token step replayed K times between CUDA events"},
+            "roofline": {"bound": "hbm", "kernel": "whole step (all linears)", "achieved": gbs, "peak": pk["hbm_gbs"] * world,
+                         "unit": "GB/s", "frac": gbs / (pk["hbm_gbs"] * world), "traffic": None,
+                         "peak_source": pk["source"], "algorithmic_bytes_per_step": nbytes},
+            "cpu_baseline": None, "e2e": None, "gpu_launches": st.launches_per_step() * args.steps, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------------
 def main():
@@ -190,7 +251,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="sweep", choices=["sweep"])
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "stack8b", "stack70b"])
+    ap.add_argument("--batch", type=int, default=1, help="batch rows for the stack workloads")
+    ap.add_argument("--layers", type=int, default=0, help="override the number of layers of a stack workload")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()
@@ -217,6 +280,12 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     pk = peaks()
+
+    if args.workload != "sweep":
+        run_stack_workload(args, qf, torch, dist, dev, world, rank, local_rank, pk)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- inputs: 5 weight copies per shape (one per M), column shard of this rank ----
     gen = torch.Generator(device=dev)
@@ -413,6 +482,16 @@ def main():
         b = algo_bytes(1, 4096, 4096)
         extra["cfg0_gemv_m1_4096x4096_f16"] = {"us": round(us, 2), "gbs": round(b / us / 1e3, 1),
                                                 "frac_hbm": round(b / us / 1e3 / pk["hbm_gbs"], 3)}
+        from quantforge_b200 import stack as S
+        for bsz in (1, 16):
+            st = S.DecodeLinearStack(S.LLAMA3_8B, bsz, torch.bfloat16, dev)
+            ms, g = time_stack(st, torch, dist, dev, 1, 20, 3)
+            nb = st.bytes_per_step()
+            extra[f"cfg2_llama3_8b_decode_linears_batch{bsz}"] = {
+                "us_per_token": round(ms * 1e3, 1), "gbs": round(nb / ms / 1e6, 1),
+                "frac_hbm": round(nb / ms / 1e6 / pk["hbm_gbs"], 3), "launches": st.launches_per_step()}
+            del st, g
+            torch.cuda.empty_cache()
         us = time_case(2048, 8192, 28672, torch.bfloat16, torch.bfloat16, True, 0.01, copies=2, reps=3)
         tf = 2.0 * 2048 * 8192 * 28672 / us / 1e6
         extra["cfg3_gemm_m2048_k8192_n28672_bf16_sym"] = {
