@@ -215,8 +215,7 @@ def run_stack_workload(args, qf, torch, dist, dev, world, rank, local_rank, pk):
     if rank == 0:
         sampler.start()
     ms, g = time_stack(st, torch, dist, dev, world, args.steps, args.warmup)
-    t_end = time.time() + 1.5
-    while time.time() < t_end:
+    for _ in range(max(1, int(1.5 / max(ms * 1e-3, 1e-6)) // 5)):  # same count on every rank (collectives inside)
         for _ in range(5):
             g.replay()
         torch.cuda.synchronize()
@@ -278,7 +277,9 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a short collective timeout turns a rank mismatch into an error instead of a hang
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     pk = peaks()
 
     if args.workload != "sweep":
@@ -364,9 +365,9 @@ def main():
     ms_total = time_graph(g_step, args.steps, args.warmup)
     launches = (len(cases)) * args.steps  # graph replays do not pass through the host launch counter
     host_launches = qf.launch_count() - launches_before
-    # keep the identical load running so that the 100 ms clock sampler sees it
-    t_end = time.time() + 1.5
-    while time.time() < t_end:
+    # keep the identical load running so that the 100 ms clock sampler sees it; the replay count is derived
+    # from the rank-agreed step time so that every rank issues the same number of collectives
+    for _ in range(max(1, int(1.5 / max(ms_total / args.steps * 1e-3, 1e-6)) // 50)):
         for _ in range(50):
             g_step.replay()
         torch.cuda.synchronize()
