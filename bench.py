@@ -529,6 +529,12 @@ def main():
             line["extra"] = extra
         print(json.dumps(line), flush=True)
     if world > 1:
+        # graphs that captured NCCL kernels must be gone before the communicator is torn down
+        del g_step, g
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
+        dist.barrier()
         dist.destroy_process_group()
 
 
