@@ -210,7 +210,8 @@ def time_stack(stack, torch, dist, dev, world, steps, warmup):
 def run_stack_workload(args, qf, torch, dist, dev, world, rank, local_rank, pk):
     from quantforge_b200 import stack as S
     cfg = S.LLAMA3_8B if args.workload == "stack8b" else S.LLAMA3_70B
-    st = S.DecodeLinearStack(cfg, args.batch, torch.bfloat16, dev, world, rank, None, args.layers or None)
+    st = S.DecodeLinearStack(cfg, args.batch, torch.bfloat16, dev, world, rank, None, args.layers or None,
+                             fuse=args.fuse)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -229,6 +230,7 @@ def run_stack_workload(args, qf, torch, dist, dev, world, rank, local_rank, pk):
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "batch": args.batch, "layers": st.L, "group_size": GROUP,
+                       "fused_qkv_gate_up": bool(args.fuse),
                        "parallelism": "single GPU" if world == 1 else
                        f"tensor parallel x{world}: column q/k/v/gate/up, row o/down + NCCL all-reduce (bf16)",
                        "l2": f"weights of the step: {nbytes / 1e9:.2f} GB, far above L2",
@@ -253,6 +255,7 @@ def main():
     ap.add_argument("--workload", default="sweep", choices=["sweep", "stack8b", "stack70b"])
     ap.add_argument("--batch", type=int, default=1, help="batch rows for the stack workloads")
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers of a stack workload")
+    ap.add_argument("--fuse", action="store_true", help="stack workloads: one launch for q/k/v and one for gate/up")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()
@@ -485,14 +488,15 @@ def main():
                                                 "frac_hbm": round(b / us / 1e3 / pk["hbm_gbs"], 3)}
         from quantforge_b200 import stack as S
         for bsz in (1, 16):
-            st = S.DecodeLinearStack(S.LLAMA3_8B, bsz, torch.bfloat16, dev)
-            ms, g = time_stack(st, torch, dist, dev, 1, 20, 3)
-            nb = st.bytes_per_step()
-            extra[f"cfg2_llama3_8b_decode_linears_batch{bsz}"] = {
-                "us_per_token": round(ms * 1e3, 1), "gbs": round(nb / ms / 1e6, 1),
-                "frac_hbm": round(nb / ms / 1e6 / pk["hbm_gbs"], 3), "launches": st.launches_per_step()}
-            del st, g
-            torch.cuda.empty_cache()
+            for fuse in (False, True):
+                st = S.DecodeLinearStack(S.LLAMA3_8B, bsz, torch.bfloat16, dev, fuse=fuse)
+                ms, g = time_stack(st, torch, dist, dev, 1, 20, 3)
+                nb = st.bytes_per_step()
+                extra[f"cfg2_llama3_8b_decode_linears_batch{bsz}" + ("_fused_qkv_gate_up" if fuse else "")] = {
+                    "us_per_token": round(ms * 1e3, 1), "gbs": round(nb / ms / 1e6, 1),
+                    "frac_hbm": round(nb / ms / 1e6 / pk["hbm_gbs"], 3), "launches": st.launches_per_step()}
+                del st, g
+                torch.cuda.empty_cache()
         us = time_case(2048, 8192, 28672, torch.bfloat16, torch.bfloat16, True, 0.01, copies=2, reps=3)
         tf = 2.0 * 2048 * 8192 * 28672 / us / 1e6
         extra["cfg3_gemm_m2048_k8192_n28672_bf16_sym"] = {

@@ -1,4 +1,5 @@
 // C ABI of the runtime (include/quantforge_rt.h): argument checks, planning, dispatch.
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -7,6 +8,14 @@
 namespace qf {
 
 std::atomic<long long> g_launch_count{0};
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char *e = std::getenv("QF_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
 
 static constexpr int kSmCount = 148;  // planning constant: the library targets B200 only
 // The split-K arrival counters occupy a FIXED region at the start of the workspace, so that a

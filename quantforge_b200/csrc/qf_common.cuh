@@ -8,6 +8,7 @@
 
 #include <atomic>
 #include <string>
+#include <utility>
 
 #include "quantforge_rt.h"
 
@@ -37,6 +38,28 @@ struct qf_ctx {
 namespace qf {
 
 extern std::atomic<long long> g_launch_count;
+
+// Programmatic dependent launch (PDL): a kernel launched with it may start while the previous kernel in the
+// stream is still draining; it must execute griddep_wait() before touching anything that kernel wrote.
+// The linear kernels use the head start for what does not depend on the previous kernel: weight streams,
+// converter constants, barrier and TMEM set-up. QF_PDL=0 in the environment turns it off.
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                 bool pdl, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 inline int fail(qf_ctx *ctx, int status, const std::string &msg) {
     if (ctx) ctx->last_error = msg;
@@ -87,6 +110,11 @@ int gemm_init(qf_ctx *ctx);
 // Device helpers: nibble -> f16 / bf16 conversion with zero and scale applied in registers.
 // ---------------------------------------------------------------------------------------------
 #ifdef __CUDACC__
+
+// PDL: wait until the previous kernel of the stream has completed and its writes are visible (no-op without PDL).
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// PDL: allow the next kernel of the stream to start its own independent prologue.
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
     uint32_t r;

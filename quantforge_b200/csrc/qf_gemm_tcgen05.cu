@@ -298,6 +298,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
     volatile int *abort_flag = &s_abort;
+    griddep_launch_dependents();  // the next kernel may begin its own set-up and weight prefetch
 
     int producer_issued = 0;  // meaningful in the elected producer lane only
     if (warp == 8) {
@@ -307,39 +308,56 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
         const uint32_t zbytes = p.zero_mode == QF_ZERO_U4 ? 64u : p.zero_mode == QF_ZERO_I8 ? 128u : 0u;
         const uint32_t tx_bytes = C::STAGE_BYTES + 256u + zbytes;
         const int group_kb = p.group_size / BK;  // k-blocks per quantisation group (>= 1)
-        int gi = kb0 / group_kb, g_rem = kb0 % group_kb;
+        const int gi = kb0 / group_kb;
         const uint8_t *sc_ptr = (const uint8_t *)(p.scales + n0) + (size_t)gi * p.N * 2;
         const size_t z_row = p.zero_mode == QF_ZERO_U4 ? (size_t)p.N / 2 : (size_t)p.N;
         const uint8_t *z_ptr =
             (const uint8_t *)p.zeros + (p.zero_mode == QF_ZERO_U4 ? (size_t)n0 / 2 : (size_t)n0) + (size_t)gi * z_row;
         const int w_row0 = p.tiled ? n_tile * (int)(p.K >> 7) * 128 : (int)n0;
-        int s = 0;
-        uint32_t ph = 0;
-        for (int it = 0; it < nkb; ++it) {
-            const bool ok = mbar_wait(empty_bar(s), ph ^ 1, abort_flag);
-            if (!__all_sync(0xffffffffu, ok)) break;
-            if (leader) {
-                const int kb = kb0 + it;
-                const uint32_t fb = full_bar(s);
-                mbar_arrive_expect_tx(fb, tx_bytes);
-                if (p.tiled) {
-                    // tile-major weights: rows of 64 bytes, the 128 rows of (n_tile, 128-code block) adjacent
-                    const int kb128 = (kb * BK) >> 7;
-                    tma_load_2d(w_stage(s), &tmap_w, fb, (BK == 128) ? 0 : (kb & 1) * 32, w_row0 + kb128 * 128);
-                } else {
-                    tma_load_2d(w_stage(s), &tmap_w, fb, kb * C::W_ROW_BYTES, w_row0);
-                }
-                bulk_load(sz_stage(s), sc_ptr, 256u, fb);
-                if (zbytes) bulk_load(sz_stage(s) + 256u, z_ptr, zbytes, fb);
-#pragma unroll
-                for (int b = 0; b < BK / 64; ++b)
-                    tma_load_2d(x_stage(s) + b * C::X_BOX_BYTES, &tmap_x, fb, kb * BK + b * 64, (int)m0);
-                producer_issued = it + 1;
+        // issue_w is called for it = 0, 1, 2, ... in order: the sliver pointers advance incrementally
+        int g_rem = kb0 % group_kb;
+        auto issue_w = [&](int it, int s) {
+            const int kb = kb0 + it;
+            const uint32_t fb = full_bar(s);
+            mbar_arrive_expect_tx(fb, tx_bytes);
+            if (p.tiled) {
+                // tile-major weights: rows of 64 bytes, the 128 rows of (n_tile, 128-code block) adjacent
+                const int kb128 = (kb * BK) >> 7;
+                tma_load_2d(w_stage(s), &tmap_w, fb, (BK == 128) ? 0 : (kb & 1) * 32, w_row0 + kb128 * 128);
+            } else {
+                tma_load_2d(w_stage(s), &tmap_w, fb, kb * C::W_ROW_BYTES, w_row0);
             }
+            bulk_load(sz_stage(s), sc_ptr, 256u, fb);
+            if (zbytes) bulk_load(sz_stage(s) + 256u, z_ptr, zbytes, fb);
             if (++g_rem == group_kb) {
                 g_rem = 0;
                 sc_ptr += (size_t)p.N * 2;
                 z_ptr += z_row;
+            }
+        };
+        auto issue_x = [&](int it, int s) {
+            const int kb = kb0 + it;
+#pragma unroll
+            for (int b = 0; b < BK / 64; ++b)
+                tma_load_2d(x_stage(s) + b * C::X_BOX_BYTES, &tmap_x, full_bar(s), kb * BK + b * 64, (int)m0);
+            producer_issued = it + 1;
+        };
+        // First pass over the ring: weights, scales and zeros do not depend on the previous kernel of the stream,
+        // so they are requested before the dependency wait; the activations after it.
+        const int npre = min(STAGES, nkb);
+        if (leader)
+            for (int it = 0; it < npre; ++it) issue_w(it, it);
+        griddep_wait();
+        if (leader)
+            for (int it = 0; it < npre; ++it) issue_x(it, it);
+        int s = npre % STAGES;
+        uint32_t ph = npre == STAGES ? 1u : 0u;
+        for (int it = npre; it < nkb; ++it) {
+            const bool ok = mbar_wait(empty_bar(s), ph ^ 1, abort_flag);
+            if (!__all_sync(0xffffffffu, ok)) break;
+            if (leader) {
+                issue_w(it, s);
+                issue_x(it, s);
             }
             if (++s == STAGES) {
                 s = 0;
@@ -616,11 +634,13 @@ static int gemm_launch_bn(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan
     p.kblocks = (int)(d->K / C::BK);
     p.kblocks_per_split = plan.chunks_per_split;
     dim3 grid((unsigned)plan.m_tiles, (unsigned)(d->N / 128), (unsigned)plan.split_k);
-    if (p.interleaved)
-        gemm_kernel<BF16, BN, true><<<grid, GEMM_THREADS, C::SMEM_BYTES, s>>>(tw, tx, p);
-    else
-        gemm_kernel<BF16, BN, false><<<grid, GEMM_THREADS, C::SMEM_BYTES, s>>>(tw, tx, p);
+    const cudaError_t le =
+        p.interleaved ? launch_kernel(gemm_kernel<BF16, BN, true>, grid, dim3(GEMM_THREADS), C::SMEM_BYTES, s,
+                                      pdl_enabled(), tw, tx, p)
+                      : launch_kernel(gemm_kernel<BF16, BN, false>, grid, dim3(GEMM_THREADS), C::SMEM_BYTES, s,
+                                      pdl_enabled(), tw, tx, p);
     g_launch_count.fetch_add(1);
+    QF_CUDA_TRY(ctx, le);
     QF_CUDA_TRY(ctx, cudaGetLastError());
     return QF_OK;
 }

@@ -101,7 +101,9 @@ __device__ __forceinline__ ZeroScale<BF16> consts_from(const uint2 e) {
     return zs;
 }
 
-template <bool BF16, int ZMODE>
+// MPAD: rows of X staged per batch tile (1, 2, 4 or 8), a compile-time constant so that the activation
+// addressing in the main loop folds into immediates.
+template <bool BF16, int ZMODE, int MPAD>
 __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __shared__ int s_is_last;
@@ -119,7 +121,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams 
     const int64_t n_blk = (int64_t)blockIdx.x * GEMV_ROWS_PER_BLOCK;
     const int64_t row_a = n_blk + warp * 16 + g;
     const bool warp_active = (n_blk + warp * 16) < p.N;  // N is a multiple of 16
-    const int m_pad = p.m_pad;
+    constexpr int m_pad = MPAD;
 
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem_raw) + (uint32_t)tid * 16u;  // + slot * 2048
     const uint32_t table = (uint32_t)__cvta_generic_to_shared(smem_raw) + GEMV_RING_BYTES;     // [chunk][64] uint2
@@ -144,13 +146,17 @@ __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams 
         const int64_t n = n_blk + r;
         uint2 ent = make_uint2(0u, 0u);
         if (n < p.N) {
-            const int64_t gi = (c0 + cl) / p.group_chunks;
+            const int64_t gi = p.group_chunks == 1 ? (c0 + cl) : (c0 + cl) / p.group_chunks;
             ZeroScale<BF16> zs;
             zs.set(load_zero<ZMODE>(p.zeros, p.zero_const, gi, n, p.N), __ldg(p.scales + gi * p.N + n));
             ent = make_uint2(zs.zsub, zs.s2);
         }
         asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(table + (uint32_t)e * 8u), "r"(ent.x), "r"(ent.y));
     }
+
+    // Everything above is independent of the previous kernel in the stream; the activations are not.
+    griddep_launch_dependents();
+    griddep_wait();
 
     // 3. activations of this K range in fragment order, zero rows beyond M
     {
@@ -181,24 +187,27 @@ __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams 
     if (warp_active) {
         // Batch columns >= m_pad of the MMA are never stored, so their lanes may read any staged row:
         // wrap g into the staged rows instead of zero-filling registers.
-        const uint32_t x_lane = xs + (uint32_t)(((g & (m_pad - 1)) * 4 + t) * 16);
-        const uint32_t tab_a = table + (uint32_t)(warp * 16 + g) * 8u;
+        uint32_t xc = xs + (uint32_t)(((g & (m_pad - 1)) * 4 + t) * 16);
+        uint32_t tab = table + (uint32_t)(warp * 16 + g) * 8u;
+        const uint32_t *ga = ra + GEMV_DEPTH * 16;  // next chunk to request
+        const uint32_t *gb = rb + GEMV_DEPTH * 16;
+#pragma unroll 1
         for (int i = 0; i < nch; ++i) {
             cp_async_wait<GEMV_DEPTH - 1>();
-            const int slot = i & (GEMV_DEPTH - 1);
-            const uint4 va = lds128g(ring + (uint32_t)(2 * slot) * 2048u);
-            const uint4 vb = lds128g(ring + (uint32_t)(2 * slot + 1) * 2048u);
+            const uint32_t slot = ring + ((uint32_t)(i & (GEMV_DEPTH - 1)) << 12);
+            const uint4 va = lds128g(slot);
+            const uint4 vb = lds128g(slot + 2048u);
             if (i + GEMV_DEPTH < nch) {
-                cp_async16(ring + (uint32_t)(2 * slot) * 2048u, ra + (i + GEMV_DEPTH) * 16);
-                cp_async16(ring + (uint32_t)(2 * slot + 1) * 2048u, rb + (i + GEMV_DEPTH) * 16);
+                cp_async16(slot, ga);
+                cp_async16(slot + 2048u, gb);
             }
             cp_async_commit();
-            const ZeroScale<BF16> za = consts_from<BF16>(lds64g(tab_a + (uint32_t)i * (GEMV_ROWS_PER_BLOCK * 8u)));
-            const ZeroScale<BF16> zb =
-                consts_from<BF16>(lds64g(tab_a + (uint32_t)i * (GEMV_ROWS_PER_BLOCK * 8u) + 64u));
+            ga += 16;
+            gb += 16;
+            const ZeroScale<BF16> za = consts_from<BF16>(lds64g(tab));
+            const ZeroScale<BF16> zb = consts_from<BF16>(lds64g(tab + 64u));
             const uint32_t wa[4] = {va.x, va.y, va.z, va.w};
             const uint32_t wb[4] = {vb.x, vb.y, vb.z, vb.w};
-            const uint32_t xc = x_lane + (uint32_t)(i * 4 * m_pad * 64);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 uint32_t pa[4], pb[4];
@@ -208,6 +217,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams 
                 mma_16816<BF16>(acc2[0], pa[0], pb[0], pa[1], pb[1], xb.x, xb.y);
                 mma_16816<BF16>(acc2[1], pa[2], pb[2], pa[3], pb[3], xb.z, xb.w);
             }
+            tab += GEMV_ROWS_PER_BLOCK * 8u;
+            xc += 4u * m_pad * 64u;
         }
     }
     cp_async_wait<0>();
@@ -264,10 +275,18 @@ __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams 
     }
 }
 
+template <bool BF16, int ZMODE, int MPAD>
+static cudaError_t set_attr1() {
+    return cudaFuncSetAttribute(gemv_kernel<BF16, ZMODE, MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)gemv_smem_bytes(GEMV_MAX_CHUNKS_PER_SPLIT, MPAD));
+}
 template <bool BF16, int ZMODE>
 static cudaError_t set_attr() {
-    return cudaFuncSetAttribute(gemv_kernel<BF16, ZMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)gemv_smem_bytes(GEMV_MAX_CHUNKS_PER_SPLIT, 8));
+    cudaError_t e = set_attr1<BF16, ZMODE, 1>();
+    if (e == cudaSuccess) e = set_attr1<BF16, ZMODE, 2>();
+    if (e == cudaSuccess) e = set_attr1<BF16, ZMODE, 4>();
+    if (e == cudaSuccess) e = set_attr1<BF16, ZMODE, 8>();
+    return e;
 }
 
 int gemv_init(qf_ctx *ctx) {
@@ -280,14 +299,20 @@ int gemv_init(qf_ctx *ctx) {
     return QF_OK;
 }
 
+template <bool BF16, int ZMODE>
+static cudaError_t gemv_dispatch_m(dim3 grid, size_t smem, cudaStream_t s, const GemvParams &p) {
+    switch (p.m_pad) {
+        case 1: return launch_kernel(gemv_kernel<BF16, ZMODE, 1>, grid, dim3(GEMV_THREADS), smem, s, pdl_enabled(), p);
+        case 2: return launch_kernel(gemv_kernel<BF16, ZMODE, 2>, grid, dim3(GEMV_THREADS), smem, s, pdl_enabled(), p);
+        case 4: return launch_kernel(gemv_kernel<BF16, ZMODE, 4>, grid, dim3(GEMV_THREADS), smem, s, pdl_enabled(), p);
+        default: return launch_kernel(gemv_kernel<BF16, ZMODE, 8>, grid, dim3(GEMV_THREADS), smem, s, pdl_enabled(), p);
+    }
+}
 template <bool BF16>
-static void gemv_dispatch(int zmode, dim3 grid, size_t smem, cudaStream_t s, const GemvParams &p) {
-    if (zmode == QF_ZERO_CONST)
-        gemv_kernel<BF16, QF_ZERO_CONST><<<grid, GEMV_THREADS, smem, s>>>(p);
-    else if (zmode == QF_ZERO_U4)
-        gemv_kernel<BF16, QF_ZERO_U4><<<grid, GEMV_THREADS, smem, s>>>(p);
-    else
-        gemv_kernel<BF16, QF_ZERO_I8><<<grid, GEMV_THREADS, smem, s>>>(p);
+static cudaError_t gemv_dispatch(int zmode, dim3 grid, size_t smem, cudaStream_t s, const GemvParams &p) {
+    if (zmode == QF_ZERO_CONST) return gemv_dispatch_m<BF16, QF_ZERO_CONST>(grid, smem, s, p);
+    if (zmode == QF_ZERO_U4) return gemv_dispatch_m<BF16, QF_ZERO_U4>(grid, smem, s, p);
+    return gemv_dispatch_m<BF16, QF_ZERO_I8>(grid, smem, s, p);
 }
 
 int launch_gemv(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
@@ -314,11 +339,10 @@ int launch_gemv(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const vo
     const int64_t m_in_tile = d->M < 8 ? d->M : 8;
     p.m_pad = m_in_tile <= 1 ? 1 : m_in_tile <= 2 ? 2 : m_in_tile <= 4 ? 4 : 8;
     const size_t smem = gemv_smem_bytes(plan.chunks_per_split, p.m_pad);
-    if (d->act_dtype == QF_BF16)
-        gemv_dispatch<true>(d->zero_mode, grid, smem, s, p);
-    else
-        gemv_dispatch<false>(d->zero_mode, grid, smem, s, p);
+    const cudaError_t le = d->act_dtype == QF_BF16 ? gemv_dispatch<true>(d->zero_mode, grid, smem, s, p)
+                                                   : gemv_dispatch<false>(d->zero_mode, grid, smem, s, p);
     g_launch_count.fetch_add(1);
+    QF_CUDA_TRY(ctx, le);
     QF_CUDA_TRY(ctx, cudaGetLastError());
     return QF_OK;
 }

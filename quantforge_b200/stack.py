@@ -40,7 +40,10 @@ def linear_bytes(M, K, N, out_bytes=2):
 
 class DecodeLinearStack:
     def __init__(self, cfg: dict, batch: int, dtype=torch.bfloat16, device=None, world: int = 1, rank: int = 0,
-                 group: Optional[dist.ProcessGroup] = None, layers: Optional[int] = None, seed: int = 0):
+                 group: Optional[dist.ProcessGroup] = None, layers: Optional[int] = None, seed: int = 0,
+                 fuse: bool = False):
+        """fuse=True runs q/k/v as ONE linear over the concatenated output rows and gate/up likewise (4 launches
+        per layer instead of 7; same weights, same bytes, same results)."""
         self.cfg, self.M, self.dtype = cfg, batch, dtype
         self.dev = device or torch.device("cuda", torch.cuda.current_device())
         self.world, self.rank, self.group = world, rank, group
@@ -50,17 +53,26 @@ class DecodeLinearStack:
         gen = torch.Generator(device=self.dev)
         gen.manual_seed(seed + 7919 * rank)
         prepack = batch > 4  # the tcgen05 kernel serves M > 4 and reads the interleaved layout
+        self.fuse = fuse
         self.layers = []
         for _ in range(self.L):
-            self.layers.append({
-                "q": _rand_linear(H // world, H, dtype, self.dev, gen, prepack),
-                "k": _rand_linear(KV // world, H, dtype, self.dev, gen, prepack),
-                "v": _rand_linear(KV // world, H, dtype, self.dev, gen, prepack),
-                "o": _rand_linear(H, H // world, dtype, self.dev, gen, prepack),
-                "gate": _rand_linear(F // world, H, dtype, self.dev, gen, prepack),
-                "up": _rand_linear(F // world, H, dtype, self.dev, gen, prepack),
-                "down": _rand_linear(H, F // world, dtype, self.dev, gen, prepack),
-            })
+            if fuse:
+                self.layers.append({
+                    "qkv": _rand_linear((H + 2 * KV) // world, H, dtype, self.dev, gen, prepack),
+                    "o": _rand_linear(H, H // world, dtype, self.dev, gen, prepack),
+                    "gate_up": _rand_linear(2 * F // world, H, dtype, self.dev, gen, prepack),
+                    "down": _rand_linear(H, F // world, dtype, self.dev, gen, prepack),
+                })
+            else:
+                self.layers.append({
+                    "q": _rand_linear(H // world, H, dtype, self.dev, gen, prepack),
+                    "k": _rand_linear(KV // world, H, dtype, self.dev, gen, prepack),
+                    "v": _rand_linear(KV // world, H, dtype, self.dev, gen, prepack),
+                    "o": _rand_linear(H, H // world, dtype, self.dev, gen, prepack),
+                    "gate": _rand_linear(F // world, H, dtype, self.dev, gen, prepack),
+                    "up": _rand_linear(F // world, H, dtype, self.dev, gen, prepack),
+                    "down": _rand_linear(H, F // world, dtype, self.dev, gen, prepack),
+                })
         M = batch
         self.h = torch.randn(M, H, device=self.dev, generator=gen).to(dtype)
         self.buf = {
@@ -71,6 +83,11 @@ class DecodeLinearStack:
             "gate": torch.empty(M, F // world, dtype=dtype, device=self.dev),
             "up": torch.empty(M, F // world, dtype=dtype, device=self.dev),
             "down": torch.empty(M, H, dtype=dtype, device=self.dev),
+            "qkv": torch.empty(M, (H + 2 * KV) // world, dtype=dtype, device=self.dev),
+            "gate_up": torch.empty(M, 2 * F // world, dtype=dtype, device=self.dev),
+            # contiguous stand-ins for the attention output and the activation output of the fused variant
+            "attn": torch.randn(M, H // world, device=self.dev, generator=gen).to(dtype),
+            "act": torch.randn(M, F // world, device=self.dev, generator=gen).to(dtype),
         }
 
     def _lin(self, w, x, out):
@@ -81,6 +98,17 @@ class DecodeLinearStack:
         b = self.buf
         h = self.h
         for ly in self.layers:
+            if self.fuse:
+                self._lin(ly["qkv"], h, b["qkv"])
+                self._lin(ly["o"], b["attn"], b["o"])
+                if self.world > 1:
+                    dist.all_reduce(b["o"], group=self.group)
+                self._lin(ly["gate_up"], b["o"], b["gate_up"])
+                self._lin(ly["down"], b["act"], b["down"])
+                if self.world > 1:
+                    dist.all_reduce(b["down"], group=self.group)
+                h = b["down"]
+                continue
             self._lin(ly["q"], h, b["q"])
             self._lin(ly["k"], h, b["k"])
             self._lin(ly["v"], h, b["v"])
@@ -109,7 +137,7 @@ class DecodeLinearStack:
         return g
 
     def launches_per_step(self) -> int:
-        return 7 * self.L
+        return (4 if self.fuse else 7) * self.L
 
     def bytes_per_step(self) -> int:
         """Algorithmic bytes of the whole (unsharded) token step."""
