@@ -109,7 +109,7 @@ int make_plan(const qf_linear_desc *d, Plan *p, std::string *why) {
         if (d->split_k > 0) {
             split = d->split_k;
         } else {
-            const int64_t slots = (int64_t)kSmCount * (bn <= 64 ? 2 : 1);
+            const int64_t slots = (int64_t)kSmCount * (bn <= 64 ? 2 : 1);  // two narrow CTAs fit one SM
             split = (int)(slots / tiles);
             if (split < 1) split = 1;
         }

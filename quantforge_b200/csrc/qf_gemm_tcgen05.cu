@@ -502,15 +502,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
         __syncthreads();
         if (s_is_last) {
             __threadfence();
+            // Sum the partial tiles in split order. Each thread owns 4 consecutive output columns (one 16-byte load
+            // per split) and keeps 4 splits in flight, so the reduction is not a chain of dependent L2 round trips.
             const int64_t Mp = (int64_t)gridDim.x * BN;
-            for (int u = tid; u < 128 * BN; u += GEMM_THREADS) {
-                const int nl = u & 127;
-                const int64_t m = m0 + (u >> 7);
+            const size_t split_stride = (size_t)Mp * p.N;
+            for (int u = tid; u < 32 * BN; u += GEMM_THREADS) {
+                const int nl = (u & 31) * 4;
+                const int64_t m = m0 + (u >> 5);
                 if (m < p.M) {
-                    float acc = 0.f;
-                    for (int sp = 0; sp < p.split_k; ++sp)
-                        acc += __ldcg(p.partial + ((int64_t)sp * Mp + m) * p.N + n0 + nl);
-                    store_out(p.Y, p.out_dtype, m * p.N + n0 + nl, acc);
+                    const float *base = p.partial + (size_t)m * p.N + n0 + nl;
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int sp0 = 0; sp0 < p.split_k; sp0 += 4) {
+                        float4 v[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            v[j] = (sp0 + j < p.split_k)
+                                       ? __ldcg(reinterpret_cast<const float4 *>(base + (size_t)(sp0 + j) * split_stride))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            acc.x += v[j].x;
+                            acc.y += v[j].y;
+                            acc.z += v[j].z;
+                            acc.w += v[j].w;
+                        }
+                    }
+                    const int64_t o = m * p.N + n0 + nl;
+                    store_out(p.Y, p.out_dtype, o, acc.x);
+                    store_out(p.Y, p.out_dtype, o + 1, acc.y);
+                    store_out(p.Y, p.out_dtype, o + 2, acc.z);
+                    store_out(p.Y, p.out_dtype, o + 3, acc.w);
                 }
             }
         }

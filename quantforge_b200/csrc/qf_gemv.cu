@@ -268,8 +268,17 @@ __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams 
         const int64_t n = n_blk + nl;
         const int64_t mm = (int64_t)mt * 8 + m;
         if (n < p.N && mm < p.M) {
+            // split order, 8 partial sums in flight at a time (not a chain of dependent L2 round trips)
+            const float *base = p.partial + mm * p.N + n;
+            const size_t split_stride = (size_t)Mp * p.N;
             float s = 0.f;
-            for (int sp = 0; sp < p.split_k; ++sp) s += __ldcg(p.partial + ((int64_t)sp * Mp + mm) * p.N + n);
+            for (int sp0 = 0; sp0 < p.split_k; sp0 += 8) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = (sp0 + j < p.split_k) ? __ldcg(base + (size_t)(sp0 + j) * split_stride) : 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) s += v[j];
+            }
             store_out(p.Y, p.out_dtype, mm * p.N + n, s);
         }
     }
