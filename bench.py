@@ -301,8 +301,8 @@ def main():
         G = K // GROUP
         for M in SWEEP_MS:
             qw = torch.randint(-128, 128, (Nl, K // 2), dtype=torch.int8, device=dev, generator=gen)
-            # one-time, untimed weight prepack for the linears the tcgen05 kernel serves (M > 4)
-            layout = LAYOUT_INTERLEAVED if (M > 4 and Nl % 128 == 0) else LAYOUT_CANONICAL
+            # one-time, untimed weight prepack for the linears the tcgen05 kernel serves (M > 2)
+            layout = LAYOUT_INTERLEAVED if (M > 2 and Nl % 128 == 0) else LAYOUT_CANONICAL
             if layout != LAYOUT_CANONICAL:
                 qw = qf.prepack_w4(qw, layout=layout)
             sc = (torch.randn(G, Nl, device=dev, generator=gen).abs() * (0.02 / 7.0)).clamp_min(2.0 ** -14).to(
@@ -379,8 +379,8 @@ def main():
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
 
     # ---- roofline of the dominant kernel: both kernel families timed alone, the one with the larger share wins ----
-    gemv_cases = [c for c in cases if c["M"] <= 4]   # qf::gemv_kernel (canonical weights)
-    gemm_cases = [c for c in cases if c["M"] > 4]    # qf::gemm_kernel (tcgen05, prepacked weights)
+    gemv_cases = [c for c in cases if c["M"] <= 2]   # qf::gemv_kernel (canonical weights)
+    gemm_cases = [c for c in cases if c["M"] > 2]    # qf::gemm_kernel (tcgen05, prepacked weights)
     roof = {}
     for name, sub in (("gemv", gemv_cases), ("gemm", gemm_cases)):
         g = make_graph(sub)
@@ -391,7 +391,7 @@ def main():
                       "share": per_launch_s * len(sub)}
     tot = roof["gemv"]["share"] + roof["gemm"]["share"]
     dom, oth = ("gemm", "gemv") if roof["gemm"]["share"] >= roof["gemv"]["share"] else ("gemv", "gemm")
-    names = {"gemv": "qf::gemv_kernel (M<=4 linears)", "gemm": "qf::gemm_kernel tcgen05 (M=8,16,64 linears)"}
+    names = {"gemv": "qf::gemv_kernel (M=1 linears)", "gemm": "qf::gemm_kernel tcgen05 (M=4,8,16,64 linears)"}
     # DRAM bytes per launch from ncu (profiles/): read+write traffic was 0.99x (gemm) / 1.00x (gemv) of the
     # algorithmic bytes on the captured cases; scaled here to the average launch of the step.
     ncu_ratio = {"gemm": 0.99, "gemv": 1.00}
@@ -439,7 +439,7 @@ def main():
         wbytes = K * N // 2
         n = copies or max(3, -(-300_000_000 // wbytes))
         G = K // GROUP
-        layout = LAYOUT_INTERLEAVED if (M > 4 and N % 128 == 0) else LAYOUT_CANONICAL
+        layout = LAYOUT_INTERLEAVED if (M > 2 and N % 128 == 0) else LAYOUT_CANONICAL
         sets = []
         for _ in range(n):
             qw = torch.randint(-128, 128, (N, K // 2), dtype=torch.int8, device=dev, generator=gen)

@@ -52,7 +52,7 @@ int make_plan(const qf_linear_desc *d, Plan *p, std::string *why) {
         if (d->reserved[i] != 0) return bad(QF_ERR_BAD_ARG, "reserved fields must be zero");
 
     int path = d->path;
-    if (path == QF_PATH_AUTO) path = (d->M <= 4) ? QF_PATH_GEMV : QF_PATH_GEMM;
+    if (path == QF_PATH_AUTO) path = (d->M <= 2) ? QF_PATH_GEMV : QF_PATH_GEMM;
     if (path != QF_PATH_GEMV && path != QF_PATH_GEMM) return bad(QF_ERR_BAD_ARG, "unknown path");
     if (path == QF_PATH_GEMM && d->N % 128 != 0) {
         if (d->path == QF_PATH_GEMM) return bad(QF_ERR_BAD_ARG, "the GEMM path needs N to be a multiple of 128");

@@ -52,7 +52,7 @@ class DecodeLinearStack:
         assert H % world == 0 and KV % world == 0 and F % world == 0
         gen = torch.Generator(device=self.dev)
         gen.manual_seed(seed + 7919 * rank)
-        prepack = batch > 4  # the tcgen05 kernel serves M > 4 and reads the interleaved layout
+        prepack = batch > 2  # the tcgen05 kernel serves M > 2 and reads the interleaved layout
         self.fuse = fuse
         self.layers = []
         for _ in range(self.L):
