@@ -211,7 +211,7 @@ def run_stack_workload(args, qf, torch, dist, dev, world, rank, local_rank, pk):
     from quantforge_b200 import stack as S
     cfg = S.LLAMA3_8B if args.workload == "stack8b" else S.LLAMA3_70B
     st = S.DecodeLinearStack(cfg, args.batch, torch.bfloat16, dev, world, rank, None, args.layers or None,
-                             fuse=args.fuse)
+                             fuse=args.fuse, fused_allreduce=args.fused_allreduce and world > 1)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -232,7 +232,9 @@ def run_stack_workload(args, qf, torch, dist, dev, world, rank, local_rank, pk):
             "config": {"workload": args.workload, "batch": args.batch, "layers": st.L, "group_size": GROUP,
                        "fused_qkv_gate_up": bool(args.fuse),
                        "parallelism": "single GPU" if world == 1 else
-                       f"tensor parallel x{world}: column q/k/v/gate/up, row o/down + NCCL all-reduce (bf16)",
+                       f"tensor parallel x{world}: column q/k/v/gate/up, row o/down + " +
+                       ("sum over ranks inside the GEMV kernel over NVLink peer memory (fp32 partials)"
+                        if st.comm is not None else "NCCL all-reduce (bf16)"),
                        "l2": f"weights of the step: {nbytes / 1e9:.2f} GB, far above L2",
                        "timing": "CUDA graph of one token step replayed K times between CUDA events"},
             "roofline": {"bound": "hbm", "kernel": "whole step (all linears)", "achieved": gbs, "peak": pk["hbm_gbs"] * world,
@@ -241,6 +243,8 @@ def run_stack_workload(args, qf, torch, dist, dev, world, rank, local_rank, pk):
             "cpu_baseline": None, "e2e": None, "gpu_launches": st.launches_per_step() * args.steps, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
+    del g
+    st.close()
 
 
 # ------------------------------------------------------------------------------------------------
@@ -256,6 +260,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1, help="batch rows for the stack workloads")
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers of a stack workload")
     ap.add_argument("--fuse", action="store_true", help="stack workloads: one launch for q/k/v and one for gate/up")
+    ap.add_argument("--fused-allreduce", action="store_true",
+                    help="stack workloads on N > 1 GPUs, batch <= 8: row-parallel linears sum over ranks inside the kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()

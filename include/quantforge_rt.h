@@ -185,6 +185,39 @@ int qf_ctx_clear_status(qf_ctx *ctx);
 int qf_w4a16_gemv_static_scratch(qf_ctx *ctx, const qf_linear_desc *desc, const void *X, const void *qweight,
                                  const void *scales, const void *qzeros_or_null, void *Y, void *stream);
 
+/*
+ * Row-parallel linear with the cross-GPU sum inside the kernel. (No counterpart in the reference, which runs on
+ * one device; the multi-GPU deployment this runtime adds would otherwise follow the linear with an NCCL all-reduce.)
+ *
+ * Each rank (one process per GPU of one node) holds the K shard [rank*K/world, (rank+1)*K/world) of the weights,
+ * scales and zeros and the matching columns of X; `desc->K` is the shard's K. Every rank receives the full sum in
+ * its own Y, bit-identical on all ranks (fp32 partial outputs are summed in rank order, then rounded once).
+ * The GEMV kernel (desc->M <= 8, canonical weights) pushes each finished block of 64 output columns into all
+ * ranks' exchange buffers with peer stores over NVLink and waits for the other ranks' pushes of the same block,
+ * so the exchange overlaps the weight streams still running and no separate collective is launched.
+ *
+ * Set-up, once per group of ranks:
+ *   qf_comm_create(ctx, rank, world, max_out_elems, &comm)   allocates this rank's exchange buffer
+ *                                                            (8 * world * max_out_elems bytes + 288 KB)
+ *   qf_comm_export(comm, handle)                             QF_COMM_HANDLE_BYTES bytes to send to every rank
+ *   qf_comm_connect(comm, handles, world)                    handles of all ranks, in rank order; maps the peers
+ *   <a barrier of the caller's own, e.g. torch.distributed.barrier()>  before the first call
+ * and a barrier again before qf_comm_destroy. world == 1 needs no handles (connect may be skipped).
+ * Rules: all ranks make the same sequence of calls on a comm; calls on one comm are stream-ordered on each rank
+ * (one stream, or serialised); desc->M * desc->N <= max_out_elems. A rank that waits longer than about a second
+ * for a peer gives up: its Y is not written, qf_ctx_status(ctx) reads QF_ERR_TIMEOUT after the stream is
+ * synchronised, and the comm must be destroyed. `workspace` as for qf_w4a16_linear with desc->path = QF_PATH_GEMV.
+ */
+typedef struct qf_comm qf_comm;
+#define QF_COMM_HANDLE_BYTES 64
+int qf_comm_create(qf_ctx *ctx, int rank, int world, size_t max_out_elems, qf_comm **out);
+int qf_comm_export(const qf_comm *comm, void *handle_out);
+int qf_comm_connect(qf_comm *comm, const void *handles, int n_handles);
+int qf_comm_destroy(qf_comm *comm);
+int qf_w4a16_linear_allreduce(qf_ctx *ctx, qf_comm *comm, const qf_linear_desc *desc, const void *X,
+                              const void *qweight, const void *scales, const void *qzeros_or_null, void *Y,
+                              void *workspace, size_t workspace_bytes, void *stream);
+
 /* Which kernel family `desc` resolves to (QF_PATH_GEMV / QF_PATH_GEMM) and the K split it will use. */
 int qf_w4a16_plan(const qf_linear_desc *desc, int32_t *path_out, int32_t *split_k_out);
 

@@ -22,7 +22,9 @@ EXPORTS = [
     "qf_version", "qf_status_string", "qf_ctx_create", "qf_ctx_destroy", "qf_last_error", "qf_unpack_int4",
     "qf_dequant_w4", "qf_w4a16_workspace_bytes", "qf_w4a16_linear", "qf_w4a16_linear_host", "qf_w4a16_plan",
     "qf_launch_count", "qf_prepack_w4", "qf_prepack_w4_tiled", "qf_w4a16_gemv_static_scratch", "qf_ctx_status", "qf_ctx_clear_status",
+    "qf_comm_create", "qf_comm_export", "qf_comm_connect", "qf_comm_destroy", "qf_w4a16_linear_allreduce",
 ]
+QF_COMM_HANDLE_BYTES = 64
 
 
 class LinearDesc(ctypes.Structure):
@@ -76,6 +78,11 @@ def load() -> ctypes.CDLL:
     lib.qf_prepack_w4_tiled.argtypes = [vp, vp, vp, i64, i64, ctypes.c_int, vp]
     lib.qf_ctx_status.argtypes = [vp]
     lib.qf_ctx_clear_status.argtypes = [vp]
+    lib.qf_comm_create.argtypes = [vp, ctypes.c_int, ctypes.c_int, sz, ctypes.POINTER(vp)]
+    lib.qf_comm_export.argtypes = [vp, vp]
+    lib.qf_comm_connect.argtypes = [vp, vp, ctypes.c_int]
+    lib.qf_comm_destroy.argtypes = [vp]
+    lib.qf_w4a16_linear_allreduce.argtypes = [vp, vp, dp, vp, vp, vp, vp, vp, vp, sz, vp]
     _lib = lib
     return lib
 

@@ -86,6 +86,26 @@ struct Plan {
     size_t ws_counter_bytes;
 };
 
+// ---------------------------------------------------------------------------------------------
+// Exchange over peer memory (row-parallel linears: partial outputs summed across GPUs inside the kernel)
+// ---------------------------------------------------------------------------------------------
+constexpr int kMaxPeers = 8;
+constexpr int kCommMaxBlocks = 8192;  // column blocks (x batch tiles) of one linear that can exchange
+
+// Kernel-side view of a qf_comm. Every rank's buffer has the same layout:
+//   seen  [kCommMaxBlocks]            u32  calls completed per column block (read and written by the owner only)
+//   flags [kCommMaxBlocks][kMaxPeers] u32  pushes received per (column block, source rank); peers add 1 per call
+//   slots [2][world][slot_elems]      f32  partial outputs, double-buffered by the parity of `seen`
+struct ArParams {
+    float *slots[kMaxPeers];      // slots region of every rank's buffer (own rank: local address)
+    unsigned *flags[kMaxPeers];   // flags region of every rank's buffer
+    unsigned *seen;               // local
+    int *status;                  // device status word of the context (bounded waits report here)
+    unsigned long long slot_elems;
+    int world;
+    int rank;
+};
+
 // Validates `d` and fills the launch plan. Returns QF_OK or an error status; `why` receives a message.
 int make_plan(const qf_linear_desc *d, Plan *p, std::string *why);
 
@@ -101,6 +121,8 @@ int launch_prepack(qf_ctx *ctx, const void *in, void *out, int64_t n_words, int 
 int launch_prepack_tiled(qf_ctx *ctx, const void *in, void *out, int64_t N, int64_t K, int to_canonical,
                          cudaStream_t s);
 int gemm_block_k(int bn);
+int launch_gemv_ar(qf_ctx *ctx, const qf_linear_desc *d, const Plan &p, const void *X, const void *qw,
+                   const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s, const ArParams &ar);
 int launch_gemv_static(qf_ctx *ctx, const qf_linear_desc *d, const Plan &p, const void *X, const void *qw,
                        const void *scales, const void *zeros, void *Y, cudaStream_t s);
 int gemv_init(qf_ctx *ctx);

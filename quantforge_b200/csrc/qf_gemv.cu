@@ -47,7 +47,19 @@ struct GemvParams {
     int out_dtype;
     int zero_const;
     int m_pad;          // rows of X staged per batch tile: 1, 2, 4 or 8
+    ArParams ar;        // read by the AR (cross-GPU sum) instantiations only
 };
+
+// system-scope flag traffic of the cross-GPU exchange
+__device__ __forceinline__ void red_add_release_sys(unsigned *ptr, unsigned v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *ptr) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+constexpr long long kExchangeWaitCycles = 2000000000LL;  // about a second; then the kernel reports QF_ERR_TIMEOUT
 
 // dynamic shared memory: ring | constants table [chunks][64 rows] uint2 | staged X [chunks][4][m_pad][4] uint4
 static inline size_t gemv_smem_bytes(int chunks_per_split, int m_pad) {
@@ -103,10 +115,20 @@ __device__ __forceinline__ ZeroScale<BF16> consts_from(const uint2 e) {
 
 // MPAD: rows of X staged per batch tile (1, 2, 4 or 8), a compile-time constant so that the activation
 // addressing in the main loop folds into immediates.
-template <bool BF16, int ZMODE, int MPAD>
+// AR: this GPU holds a K shard of the weights (row-parallel linear). The block that finishes a column block
+// pushes its 64 x M fp32 partial outputs into every rank's slot with peer stores, raises a per-(column block,
+// source) counter on every rank, waits (bounded) until all ranks' pushes for the same column block have arrived
+// here, sums the slots in rank order (same bits on every rank) and writes Y. The exchange of a column block
+// overlaps the weight streams of the blocks still running; no separate all-reduce kernel follows.
+// A waiting block depends only on blocks that the peers dispatched before their own waiting blocks (blocks are
+// dispatched in index order and a block waits only after every block of its column has arrived), so waiters
+// cannot starve the work they wait for; the wait is bounded all the same.
+template <bool BF16, int ZMODE, int MPAD, bool AR = false>
 __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __shared__ int s_is_last;
+    __shared__ int s_ar_fail;
+    __shared__ float s_tile[AR ? 8 * GEMV_ROWS_PER_BLOCK : 1];  // [batch row][column] of the finished column block
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -228,7 +250,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams 
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[i] = acc2[0][i] + acc2[1][i];
     const int64_t m0 = (int64_t)mt * 8 + 2 * t;
-    if (p.split_k == 1) {
+    if (!AR && p.split_k == 1) {
         if (warp_active) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
@@ -241,53 +263,127 @@ __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams 
         return;
     }
 
-    const int64_t Mp = (int64_t)gridDim.z * 8;
-    if (warp_active && 2 * t < m_pad) {
-        float *dst = p.partial + ((int64_t)split * Mp + m0) * p.N;
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            __stcg(dst + e * p.N + row_a, acc[e]);
-            __stcg(dst + e * p.N + row_a + 8, acc[2 + e]);
-        }
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        int *cnt = p.counters + blockIdx.z * gridDim.x + blockIdx.x;
-        const int prev = atomicAdd(cnt, 1);
-        s_is_last = (prev == p.split_k - 1);
-        if (s_is_last) *cnt = 0;  // ready for the next launch
-    }
-    __syncthreads();
-    if (!s_is_last) return;
-    __threadfence();
     const int m_rows = min(8, m_pad + (m_pad & 1));  // rows of this batch tile that hold partial sums
-    for (int u = tid; u < GEMV_ROWS_PER_BLOCK * m_rows; u += GEMV_THREADS) {
-        const int nl = u & (GEMV_ROWS_PER_BLOCK - 1);
-        const int m = u / GEMV_ROWS_PER_BLOCK;
-        const int64_t n = n_blk + nl;
-        const int64_t mm = (int64_t)mt * 8 + m;
-        if (n < p.N && mm < p.M) {
-            // split order, 8 partial sums in flight at a time (not a chain of dependent L2 round trips)
-            const float *base = p.partial + mm * p.N + n;
-            const size_t split_stride = (size_t)Mp * p.N;
-            float s = 0.f;
-            for (int sp0 = 0; sp0 < p.split_k; sp0 += 8) {
-                float v[8];
+    if (AR && p.split_k == 1) {
+        if (warp_active && 2 * t < m_pad) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = (sp0 + j < p.split_k) ? __ldcg(base + (size_t)(sp0 + j) * split_stride) : 0.f;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) s += v[j];
+            for (int e = 0; e < 2; ++e) {
+                s_tile[(2 * t + e) * GEMV_ROWS_PER_BLOCK + warp * 16 + g] = acc[e];
+                s_tile[(2 * t + e) * GEMV_ROWS_PER_BLOCK + warp * 16 + g + 8] = acc[2 + e];
             }
-            store_out(p.Y, p.out_dtype, mm * p.N + n, s);
         }
+        __syncthreads();
+    } else {
+        const int64_t Mp = (int64_t)gridDim.z * 8;
+        if (warp_active && 2 * t < m_pad) {
+            float *dst = p.partial + ((int64_t)split * Mp + m0) * p.N;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                __stcg(dst + e * p.N + row_a, acc[e]);
+                __stcg(dst + e * p.N + row_a + 8, acc[2 + e]);
+            }
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            int *cnt = p.counters + blockIdx.z * gridDim.x + blockIdx.x;
+            const int prev = atomicAdd(cnt, 1);
+            s_is_last = (prev == p.split_k - 1);
+            if (s_is_last) *cnt = 0;  // ready for the next launch
+        }
+        __syncthreads();
+        if (!s_is_last) return;
+        __threadfence();
+        for (int u = tid; u < GEMV_ROWS_PER_BLOCK * m_rows; u += GEMV_THREADS) {
+            const int nl = u & (GEMV_ROWS_PER_BLOCK - 1);
+            const int m = u / GEMV_ROWS_PER_BLOCK;
+            const int64_t n = n_blk + nl;
+            const int64_t mm = (int64_t)mt * 8 + m;
+            if (n < p.N && mm < p.M) {
+                // split order, 8 partial sums in flight at a time (not a chain of dependent L2 round trips)
+                const float *base = p.partial + mm * p.N + n;
+                const size_t split_stride = (size_t)Mp * p.N;
+                float s = 0.f;
+                for (int sp0 = 0; sp0 < p.split_k; sp0 += 8) {
+                    float v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = (sp0 + j < p.split_k) ? __ldcg(base + (size_t)(sp0 + j) * split_stride) : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) s += v[j];
+                }
+                if constexpr (AR) s_tile[u] = s;
+                else store_out(p.Y, p.out_dtype, mm * p.N + n, s);
+            }
+        }
+        if (AR) __syncthreads();
+    }
+
+    if constexpr (AR) {
+        const ArParams &ar = p.ar;
+        const int cb = blockIdx.z * gridDim.x + blockIdx.x;
+        const unsigned c = ar.seen[cb];  // calls this column block has completed on this comm (same on every rank)
+        const size_t par_off = (size_t)(c & 1u) * (size_t)ar.world * ar.slot_elems;
+        if (tid == 0) s_ar_fail = 0;
+        // 1. push this rank's partial outputs into slot [parity][rank] of every rank (own included)
+        for (int u = tid; u < GEMV_ROWS_PER_BLOCK * m_rows; u += GEMV_THREADS) {
+            const int nl = u & (GEMV_ROWS_PER_BLOCK - 1);
+            const int64_t n = n_blk + nl;
+            const int64_t mm = (int64_t)mt * 8 + u / GEMV_ROWS_PER_BLOCK;
+            if (n < p.N && mm < p.M) {
+                const float v = s_tile[u];
+                const size_t off = par_off + (size_t)ar.rank * ar.slot_elems + (size_t)(mm * p.N + n);
+                for (int r = 0; r < ar.world; ++r) __stcg(ar.slots[r] + off, v);
+            }
+        }
+        __threadfence_system();
+        __syncthreads();
+        // 2. tell every rank; 3. wait for every rank's push of this column block
+        if (tid < ar.world) {
+            red_add_release_sys(ar.flags[tid] + (size_t)cb * kMaxPeers + ar.rank, 1u);
+            const unsigned *f = ar.flags[ar.rank] + (size_t)cb * kMaxPeers + tid;
+            const long long t0 = clock64();
+            while ((int)(ld_acquire_sys(f) - (c + 1u)) < 0) {
+                __nanosleep(100);
+                if (clock64() - t0 > kExchangeWaitCycles) {
+                    s_ar_fail = 1;
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+        if (s_ar_fail) {
+            if (tid == 0) atomicExch(ar.status, QF_ERR_TIMEOUT);
+            return;
+        }
+        // 4. sum the slots in rank order and write the output
+        for (int u = tid; u < GEMV_ROWS_PER_BLOCK * m_rows; u += GEMV_THREADS) {
+            const int nl = u & (GEMV_ROWS_PER_BLOCK - 1);
+            const int64_t n = n_blk + nl;
+            const int64_t mm = (int64_t)mt * 8 + u / GEMV_ROWS_PER_BLOCK;
+            if (n < p.N && mm < p.M) {
+                const float *src = ar.slots[ar.rank] + par_off + (size_t)(mm * p.N + n);
+                float v[kMaxPeers];
+#pragma unroll
+                for (int r = 0; r < kMaxPeers; ++r) v[r] = (r < ar.world) ? __ldcg(src + (size_t)r * ar.slot_elems) : 0.f;
+                float s = 0.f;
+#pragma unroll
+                for (int r = 0; r < kMaxPeers; ++r) s += v[r];
+                store_out(p.Y, p.out_dtype, mm * p.N + n, s);
+            }
+        }
+        if (tid == 0) ar.seen[cb] = c + 1u;
     }
 }
 
 template <bool BF16, int ZMODE, int MPAD>
 static cudaError_t set_attr1() {
-    return cudaFuncSetAttribute(gemv_kernel<BF16, ZMODE, MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)gemv_smem_bytes(GEMV_MAX_CHUNKS_PER_SPLIT, MPAD));
+    const int bytes = (int)gemv_smem_bytes(GEMV_MAX_CHUNKS_PER_SPLIT, MPAD);
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<BF16, ZMODE, MPAD, false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemv_kernel<BF16, ZMODE, MPAD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 bytes);
+    return e;
 }
 template <bool BF16, int ZMODE>
 static cudaError_t set_attr() {
@@ -308,25 +404,32 @@ int gemv_init(qf_ctx *ctx) {
     return QF_OK;
 }
 
-template <bool BF16, int ZMODE>
+template <bool BF16, int ZMODE, bool AR>
 static cudaError_t gemv_dispatch_m(dim3 grid, size_t smem, cudaStream_t s, const GemvParams &p) {
+    const dim3 blk(GEMV_THREADS);
     switch (p.m_pad) {
-        case 1: return launch_kernel(gemv_kernel<BF16, ZMODE, 1>, grid, dim3(GEMV_THREADS), smem, s, pdl_enabled(), p);
-        case 2: return launch_kernel(gemv_kernel<BF16, ZMODE, 2>, grid, dim3(GEMV_THREADS), smem, s, pdl_enabled(), p);
-        case 4: return launch_kernel(gemv_kernel<BF16, ZMODE, 4>, grid, dim3(GEMV_THREADS), smem, s, pdl_enabled(), p);
-        default: return launch_kernel(gemv_kernel<BF16, ZMODE, 8>, grid, dim3(GEMV_THREADS), smem, s, pdl_enabled(), p);
+        case 1: return launch_kernel(gemv_kernel<BF16, ZMODE, 1, AR>, grid, blk, smem, s, pdl_enabled(), p);
+        case 2: return launch_kernel(gemv_kernel<BF16, ZMODE, 2, AR>, grid, blk, smem, s, pdl_enabled(), p);
+        case 4: return launch_kernel(gemv_kernel<BF16, ZMODE, 4, AR>, grid, blk, smem, s, pdl_enabled(), p);
+        default: return launch_kernel(gemv_kernel<BF16, ZMODE, 8, AR>, grid, blk, smem, s, pdl_enabled(), p);
     }
 }
+template <bool BF16, bool AR>
+static cudaError_t gemv_dispatch_z(int zmode, dim3 grid, size_t smem, cudaStream_t s, const GemvParams &p) {
+    if (zmode == QF_ZERO_CONST) return gemv_dispatch_m<BF16, QF_ZERO_CONST, AR>(grid, smem, s, p);
+    if (zmode == QF_ZERO_U4) return gemv_dispatch_m<BF16, QF_ZERO_U4, AR>(grid, smem, s, p);
+    return gemv_dispatch_m<BF16, QF_ZERO_I8, AR>(grid, smem, s, p);
+}
 template <bool BF16>
-static cudaError_t gemv_dispatch(int zmode, dim3 grid, size_t smem, cudaStream_t s, const GemvParams &p) {
-    if (zmode == QF_ZERO_CONST) return gemv_dispatch_m<BF16, QF_ZERO_CONST>(grid, smem, s, p);
-    if (zmode == QF_ZERO_U4) return gemv_dispatch_m<BF16, QF_ZERO_U4>(grid, smem, s, p);
-    return gemv_dispatch_m<BF16, QF_ZERO_I8>(grid, smem, s, p);
+static cudaError_t gemv_dispatch(int zmode, dim3 grid, size_t smem, cudaStream_t s, const GemvParams &p, bool ar) {
+    return ar ? gemv_dispatch_z<BF16, true>(zmode, grid, smem, s, p) : gemv_dispatch_z<BF16, false>(zmode, grid, smem, s, p);
 }
 
-int launch_gemv(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
-                const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s) {
+static int launch_gemv_impl(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
+                            const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s,
+                            const ArParams *ar) {
     GemvParams p;
+    p.ar = ar ? *ar : ArParams{};
     p.X = (const uint16_t *)X;
     p.qw = (const uint32_t *)qw;
     p.scales = (const uint16_t *)scales;
@@ -348,12 +451,22 @@ int launch_gemv(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const vo
     const int64_t m_in_tile = d->M < 8 ? d->M : 8;
     p.m_pad = m_in_tile <= 1 ? 1 : m_in_tile <= 2 ? 2 : m_in_tile <= 4 ? 4 : 8;
     const size_t smem = gemv_smem_bytes(plan.chunks_per_split, p.m_pad);
-    const cudaError_t le = d->act_dtype == QF_BF16 ? gemv_dispatch<true>(d->zero_mode, grid, smem, s, p)
-                                                   : gemv_dispatch<false>(d->zero_mode, grid, smem, s, p);
+    const cudaError_t le = d->act_dtype == QF_BF16 ? gemv_dispatch<true>(d->zero_mode, grid, smem, s, p, ar != nullptr)
+                                                   : gemv_dispatch<false>(d->zero_mode, grid, smem, s, p, ar != nullptr);
     g_launch_count.fetch_add(1);
     QF_CUDA_TRY(ctx, le);
     QF_CUDA_TRY(ctx, cudaGetLastError());
     return QF_OK;
+}
+
+int launch_gemv(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
+                const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s) {
+    return launch_gemv_impl(ctx, d, plan, X, qw, scales, zeros, Y, ws, s, nullptr);
+}
+
+int launch_gemv_ar(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
+                   const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s, const ArParams &ar) {
+    return launch_gemv_impl(ctx, d, plan, X, qw, scales, zeros, Y, ws, s, &ar);
 }
 
 // ---------------------------------------------------------------------------------------------

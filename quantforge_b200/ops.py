@@ -14,7 +14,7 @@ import torch
 
 from . import _lib
 from ._lib import (QF_BF16, QF_F16, QF_F32, QF_LAYOUT_CANONICAL, QF_LAYOUT_INTERLEAVED, QF_LAYOUT_TILED, QF_PATH_AUTO,
-                   QF_ZERO_CONST, QF_ZERO_I8, QF_ZERO_U4, LinearDesc, QuantForgeError)
+                   QF_PATH_GEMV, QF_ZERO_CONST, QF_ZERO_I8, QF_ZERO_U4, LinearDesc, QuantForgeError)
 
 _DT = {torch.float16: QF_F16, torch.bfloat16: QF_BF16, torch.float32: QF_F32}
 _ctxs: dict[int, ctypes.c_void_p] = {}
@@ -202,6 +202,83 @@ def w4a16_linear(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, z
         ws = _workspace(dev, workspace_bytes(d))
         st = _lib.load().qf_w4a16_linear(ctx, ctypes.byref(d), _ptr(x), _ptr(qweight), _ptr(scales), _ptr(zeros),
                                          _ptr(out), _ptr(ws), ws.numel() if ws is not None else 0, _stream(dev))
+    _check(st, ctx)
+    return out
+
+
+class Comm:
+    """Exchange buffers of a group of ranks (one process per GPU of one node) for `w4a16_linear_allreduce`.
+
+    `exchange(handle_bytes) -> list of every rank's handle bytes, in rank order` is how the 64-byte buffer handles
+    travel; by default torch.distributed.all_gather_object over `group`. The constructor ends with a barrier.
+    """
+
+    def __init__(self, max_out_elems: int, device: Optional[torch.device] = None, group=None,
+                 rank: Optional[int] = None, world: Optional[int] = None, exchange=None):
+        import torch.distributed as dist
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        if self.device.type != "cuda":
+            raise ValueError("Comm needs a CUDA device (no CPU fallback exists)")
+        use_dist = (rank is None or world is None)
+        self.group = group
+        self.rank = dist.get_rank(group) if use_dist else rank
+        self.world = dist.get_world_size(group) if use_dist else world
+        self.max_out_elems = int(max_out_elems)
+        self._ctx = _ctx(self.device)
+        self._h = ctypes.c_void_p()
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            _check(lib.qf_comm_create(self._ctx, self.rank, self.world, self.max_out_elems, ctypes.byref(self._h)),
+                   self._ctx)
+            if self.world > 1:
+                buf = ctypes.create_string_buffer(_lib.QF_COMM_HANDLE_BYTES)
+                _check(lib.qf_comm_export(self._h, buf), self._ctx)
+                mine = bytes(buf.raw)
+                if exchange is not None:
+                    handles = exchange(mine)
+                else:
+                    handles = [None] * self.world
+                    dist.all_gather_object(handles, mine, group=group)
+                blob = b"".join(handles)
+                _check(lib.qf_comm_connect(self._h, blob, self.world), self._ctx)
+                if exchange is None:
+                    dist.barrier(group=group)
+
+    def close(self, barrier: bool = True) -> None:
+        """Unmap the peers and free the buffer. Every rank must have finished its calls: with `barrier` (default)
+        the device is synchronised and the ranks meet in a torch.distributed barrier first."""
+        if self._h:
+            if self.world > 1 and barrier:
+                import torch.distributed as dist
+                torch.cuda.synchronize(self.device)
+                dist.barrier(group=self.group)
+            _lib.load().qf_comm_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+
+def w4a16_linear_allreduce(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
+                           zeros: Optional[torch.Tensor], comm: Comm, group_size: int = 128, zero_const: int = 8,
+                           out_dtype: Optional[torch.dtype] = None, split_k: int = 0,
+                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row-parallel linear: this rank's K shard of X and of the weights in, the sum over all ranks out (on every
+    rank, bit-identical), summed inside the GEMV kernel over NVLink peer memory. M <= 8, canonical weights."""
+    dev = _need_cuda(x, qweight, scales, zeros)
+    M, N, K = _check_linear_tensors(x, qweight, scales, zeros, group_size)
+    out_dtype = out_dtype or x.dtype
+    x, qweight, scales = x.contiguous(), qweight.contiguous(), scales.contiguous()
+    zeros = zeros.contiguous() if zeros is not None else None
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=dev)
+    elif tuple(out.shape) != (M, N) or out.dtype != out_dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [M, N] tensor of out_dtype")
+    d = _make_desc(M, N, K, group_size, x.dtype, out_dtype, zeros, zero_const, QF_PATH_GEMV, split_k,
+                   QF_LAYOUT_CANONICAL)
+    ctx = _ctx(dev)
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, workspace_bytes(d))
+        st = _lib.load().qf_w4a16_linear_allreduce(ctx, comm._h, ctypes.byref(d), _ptr(x), _ptr(qweight),
+                                                   _ptr(scales), _ptr(zeros), _ptr(out), _ptr(ws),
+                                                   ws.numel() if ws is not None else 0, _stream(dev))
     _check(st, ctx)
     return out
 

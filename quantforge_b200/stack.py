@@ -41,9 +41,11 @@ def linear_bytes(M, K, N, out_bytes=2):
 class DecodeLinearStack:
     def __init__(self, cfg: dict, batch: int, dtype=torch.bfloat16, device=None, world: int = 1, rank: int = 0,
                  group: Optional[dist.ProcessGroup] = None, layers: Optional[int] = None, seed: int = 0,
-                 fuse: bool = False):
+                 fuse: bool = False, fused_allreduce: bool = False):
         """fuse=True runs q/k/v as ONE linear over the concatenated output rows and gate/up likewise (4 launches
-        per layer instead of 7; same weights, same bytes, same results)."""
+        per layer instead of 7; same weights, same bytes, same results).
+        fused_allreduce=True (world > 1, batch <= 8): the row-parallel o and down linears sum across ranks inside
+        the GEMV kernel over peer memory instead of being followed by an NCCL all-reduce."""
         self.cfg, self.M, self.dtype = cfg, batch, dtype
         self.dev = device or torch.device("cuda", torch.cuda.current_device())
         self.world, self.rank, self.group = world, rank, group
@@ -54,24 +56,30 @@ class DecodeLinearStack:
         gen.manual_seed(seed + 7919 * rank)
         prepack = batch > 2  # the tcgen05 kernel serves M > 2 and reads the interleaved layout
         self.fuse = fuse
+        self.comm = None
+        if fused_allreduce and world > 1:
+            if batch > 8:
+                raise ValueError("fused_allreduce needs batch <= 8 (GEMV kernel)")
+            self.comm = ops.Comm(batch * H, device=self.dev, group=group)
+        prepack_row = prepack and self.comm is None  # the GEMV kernel reads canonical weights
         self.layers = []
         for _ in range(self.L):
             if fuse:
                 self.layers.append({
                     "qkv": _rand_linear((H + 2 * KV) // world, H, dtype, self.dev, gen, prepack),
-                    "o": _rand_linear(H, H // world, dtype, self.dev, gen, prepack),
+                    "o": _rand_linear(H, H // world, dtype, self.dev, gen, prepack_row),
                     "gate_up": _rand_linear(2 * F // world, H, dtype, self.dev, gen, prepack),
-                    "down": _rand_linear(H, F // world, dtype, self.dev, gen, prepack),
+                    "down": _rand_linear(H, F // world, dtype, self.dev, gen, prepack_row),
                 })
             else:
                 self.layers.append({
                     "q": _rand_linear(H // world, H, dtype, self.dev, gen, prepack),
                     "k": _rand_linear(KV // world, H, dtype, self.dev, gen, prepack),
                     "v": _rand_linear(KV // world, H, dtype, self.dev, gen, prepack),
-                    "o": _rand_linear(H, H // world, dtype, self.dev, gen, prepack),
+                    "o": _rand_linear(H, H // world, dtype, self.dev, gen, prepack_row),
                     "gate": _rand_linear(F // world, H, dtype, self.dev, gen, prepack),
                     "up": _rand_linear(F // world, H, dtype, self.dev, gen, prepack),
-                    "down": _rand_linear(H, F // world, dtype, self.dev, gen, prepack),
+                    "down": _rand_linear(H, F // world, dtype, self.dev, gen, prepack_row),
                 })
         M = batch
         self.h = torch.randn(M, H, device=self.dev, generator=gen).to(dtype)
@@ -93,6 +101,20 @@ class DecodeLinearStack:
     def _lin(self, w, x, out):
         ops.w4a16_linear(x, w["qw"], w["sc"], w["zr"], group_size=GROUP, out=out, weight_layout=w["layout"])
 
+    def _row(self, w, x, out):
+        """Row-parallel linear + sum over ranks."""
+        if self.comm is not None:
+            ops.w4a16_linear_allreduce(x, w["qw"], w["sc"], w["zr"], self.comm, group_size=GROUP, out=out)
+            return
+        self._lin(w, x, out)
+        if self.world > 1:
+            dist.all_reduce(out, group=self.group)
+
+    def close(self):
+        if self.comm is not None:
+            self.comm.close()
+            self.comm = None
+
     def step(self) -> torch.Tensor:
         """One token step through all layers; returns the last hidden state buffer."""
         b = self.buf
@@ -100,26 +122,18 @@ class DecodeLinearStack:
         for ly in self.layers:
             if self.fuse:
                 self._lin(ly["qkv"], h, b["qkv"])
-                self._lin(ly["o"], b["attn"], b["o"])
-                if self.world > 1:
-                    dist.all_reduce(b["o"], group=self.group)
+                self._row(ly["o"], b["attn"], b["o"])
                 self._lin(ly["gate_up"], b["o"], b["gate_up"])
-                self._lin(ly["down"], b["act"], b["down"])
-                if self.world > 1:
-                    dist.all_reduce(b["down"], group=self.group)
+                self._row(ly["down"], b["act"], b["down"])
                 h = b["down"]
                 continue
             self._lin(ly["q"], h, b["q"])
             self._lin(ly["k"], h, b["k"])
             self._lin(ly["v"], h, b["v"])
-            self._lin(ly["o"], b["q"], b["o"])            # row-parallel: partial sums
-            if self.world > 1:
-                dist.all_reduce(b["o"], group=self.group)
+            self._row(ly["o"], b["q"], b["o"])            # row-parallel: partial sums, summed over ranks
             self._lin(ly["gate"], b["o"], b["gate"])
             self._lin(ly["up"], b["o"], b["up"])
-            self._lin(ly["down"], b["gate"], b["down"])   # row-parallel: partial sums
-            if self.world > 1:
-                dist.all_reduce(b["down"], group=self.group)
+            self._row(ly["down"], b["gate"], b["down"])   # row-parallel: partial sums, summed over ranks
             h = b["down"]
         return h
 

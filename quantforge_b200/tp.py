@@ -98,12 +98,17 @@ class ColumnParallelLinear:
 
 
 class RowParallelLinear:
-    """y = sum_r x[:, K_r] . W[:, K_r]^T ; partial sums are all-reduced in fp32 (or `reduce_dtype`)."""
+    """y = sum_r x[:, K_r] . W[:, K_r]^T ; partial sums are all-reduced in fp32 (or `reduce_dtype`).
+
+    With `comm` (an `ops.Comm` of the same ranks) and M <= 8 the sum over ranks happens inside the GEMV kernel
+    over NVLink peer memory (fp32 partials, rank order, one rounding) and no NCCL collective is issued.
+    """
 
     def __init__(self, qweight, scales, zeros=None, group_size: int = 128, zero_const: int = 8,
                  group: Optional[dist.ProcessGroup] = None, input_is_parallel: bool = True,
                  reduce_dtype: torch.dtype = torch.float32, compute: Optional[Callable] = None,
-                 prepack: bool = False):
+                 prepack: bool = False, comm: Optional["ops.Comm"] = None):
+        self.comm = comm
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -122,6 +127,10 @@ class RowParallelLinear:
         out_dtype = out_dtype or x.dtype
         if not self.input_is_parallel:
             x = x[:, self.rank * self.K_local:(self.rank + 1) * self.K_local].contiguous()
+        if (self.comm is not None and self.compute is None and x.shape[0] <= 8 and
+                self.weight_layout == ops.QF_LAYOUT_CANONICAL):
+            return ops.w4a16_linear_allreduce(x, self.qweight, self.scales, self.zeros, self.comm, self.group_size,
+                                              self.zero_const, out_dtype)
         if self.compute is not None:
             y = self.compute(x, self.qweight, self.scales, self.zeros, self.group_size, self.zero_const,
                              self.reduce_dtype)
