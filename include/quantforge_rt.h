@@ -193,17 +193,18 @@ int qf_w4a16_gemv_static_scratch(qf_ctx *ctx, const qf_linear_desc *desc, const 
  * scales and zeros and the matching columns of X; `desc->K` is the shard's K. Every rank receives the full sum in
  * its own Y, bit-identical on all ranks (fp32 partial outputs are summed in rank order, then rounded once).
  * The GEMV kernel (desc->M <= 8, canonical weights) pushes each finished block of 64 output columns into all
- * ranks' exchange buffers with peer stores over NVLink and waits for the other ranks' pushes of the same block,
- * so the exchange overlaps the weight streams still running and no separate collective is launched.
+ * ranks' exchange buffers with peer stores over NVLink (value and arrival token in one 8-byte store) and polls
+ * for the other ranks' pushes of the same block, so the exchange overlaps the weight streams still running and
+ * no separate collective is launched.
  *
  * Set-up, once per group of ranks:
  *   qf_comm_create(ctx, rank, world, max_out_elems, &comm)   allocates this rank's exchange buffer
- *                                                            (8 * world * max_out_elems bytes + 288 KB)
+ *                                                            (16 * world * max_out_elems bytes + 256)
  *   qf_comm_export(comm, handle)                             QF_COMM_HANDLE_BYTES bytes to send to every rank
  *   qf_comm_connect(comm, handles, world)                    handles of all ranks, in rank order; maps the peers
  *   <a barrier of the caller's own, e.g. torch.distributed.barrier()>  before the first call
  * and a barrier again before qf_comm_destroy. world == 1 needs no handles (connect may be skipped).
- * Rules: all ranks make the same sequence of calls on a comm; calls on one comm are stream-ordered on each rank
+ * Rules: all ranks make the same sequence of calls on a comm (any mix of shapes); calls on one comm are stream-ordered on each rank
  * (one stream, or serialised); desc->M * desc->N <= max_out_elems. A rank that waits longer than about a second
  * for a peer gives up: its Y is not written, qf_ctx_status(ctx) reads QF_ERR_TIMEOUT after the stream is
  * synchronised, and the comm must be destroyed. `workspace` as for qf_w4a16_linear with desc->path = QF_PATH_GEMV.

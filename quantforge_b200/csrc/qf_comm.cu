@@ -20,17 +20,11 @@ struct qf_comm {
 
 namespace qf {
 
-static size_t comm_seen_bytes() { return (size_t)kCommMaxBlocks * sizeof(unsigned); }
-static size_t comm_flags_bytes() { return (size_t)kCommMaxBlocks * kMaxPeers * sizeof(unsigned); }
-
 static ArParams comm_params(const qf_comm *c) {
     ArParams ar = {};
-    for (int r = 0; r < c->world; ++r) {
-        char *base = (char *)c->peer[r];
-        ar.flags[r] = (unsigned *)(base + comm_seen_bytes());
-        ar.slots[r] = (float *)(base + comm_seen_bytes() + comm_flags_bytes());
-    }
-    ar.seen = (unsigned *)c->local;
+    for (int r = 0; r < c->world; ++r) ar.slots[r] = (uint2 *)((char *)c->peer[r] + kCommHeaderBytes);
+    ar.epoch = (unsigned *)c->local;
+    ar.done = (unsigned *)c->local + 1;
     ar.status = c->ctx->dev_status;
     ar.slot_elems = c->slot_elems;
     ar.world = c->world;
@@ -58,7 +52,7 @@ int qf_comm_create(qf_ctx *ctx, int rank, int world, size_t max_out_elems, qf_co
     c->rank = rank;
     c->world = world;
     c->slot_elems = (max_out_elems + 63) & ~(size_t)63;
-    c->bytes = comm_seen_bytes() + comm_flags_bytes() + (size_t)2 * world * c->slot_elems * sizeof(float);
+    c->bytes = kCommHeaderBytes + (size_t)2 * world * c->slot_elems * sizeof(uint2);
     cudaError_t e = cudaMalloc(&c->local, c->bytes);
     if (e == cudaSuccess) e = cudaMemset(c->local, 0, c->bytes);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
@@ -141,8 +135,6 @@ int qf_w4a16_linear_allreduce(qf_ctx *ctx, qf_comm *comm, const qf_linear_desc *
         return fail(ctx, QF_ERR_BAD_ARG, "device pointers must be 16-byte aligned");
     if ((size_t)d.M * (size_t)d.N > comm->slot_elems)
         return fail(ctx, QF_ERR_WORKSPACE, "M*N exceeds the max_out_elems this comm was created with");
-    const int64_t blocks = ((d.N + 63) / 64) * plan.m_tiles;
-    if (blocks > kCommMaxBlocks) return fail(ctx, QF_ERR_UNSUPPORTED, "N too large for the exchange (N <= 524288)");
     const size_t need = plan.ws_partial_bytes + plan.ws_counter_bytes;
     if (need > 0) {
         if (!workspace || workspace_bytes < need)

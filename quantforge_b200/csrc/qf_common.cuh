@@ -90,16 +90,19 @@ struct Plan {
 // Exchange over peer memory (row-parallel linears: partial outputs summed across GPUs inside the kernel)
 // ---------------------------------------------------------------------------------------------
 constexpr int kMaxPeers = 8;
-constexpr int kCommMaxBlocks = 8192;  // column blocks (x batch tiles) of one linear that can exchange
+constexpr size_t kCommHeaderBytes = 256;  // epoch, done, padding
 
 // Kernel-side view of a qf_comm. Every rank's buffer has the same layout:
-//   seen  [kCommMaxBlocks]            u32  calls completed per column block (read and written by the owner only)
-//   flags [kCommMaxBlocks][kMaxPeers] u32  pushes received per (column block, source rank); peers add 1 per call
-//   slots [2][world][slot_elems]      f32  partial outputs, double-buffered by the parity of `seen`
+//   epoch                          u32   calls completed on this comm (advanced by the last block of each call)
+//   done                           u32   column blocks of the running call that have finished
+//   slots [2][world][slot_elems]   (f32 value, u32 token) pairs, double-buffered by the parity of the epoch
+// Slot [parity][src] of rank r is written by rank src only (peer stores) and read by rank r only.
+// Why two buffers are enough: a rank starts call k+2 only after it finished call k+1, which needed every
+// rank's pushes of call k+1, and a rank pushes for call k+1 only after its own call k (and its reads) finished.
 struct ArParams {
-    float *slots[kMaxPeers];      // slots region of every rank's buffer (own rank: local address)
-    unsigned *flags[kMaxPeers];   // flags region of every rank's buffer
-    unsigned *seen;               // local
+    uint2 *slots[kMaxPeers];      // slots region of every rank's buffer (own rank: local address)
+    unsigned *epoch;              // local
+    unsigned *done;               // local
     int *status;                  // device status word of the context (bounded waits report here)
     unsigned long long slot_elems;
     int world;

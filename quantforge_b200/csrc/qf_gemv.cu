@@ -50,13 +50,13 @@ struct GemvParams {
     ArParams ar;        // read by the AR (cross-GPU sum) instantiations only
 };
 
-// system-scope flag traffic of the cross-GPU exchange
-__device__ __forceinline__ void red_add_release_sys(unsigned *ptr, unsigned v) {
-    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+// cross-GPU exchange: 8-byte (value, token) pairs, written and read whole
+__device__ __forceinline__ void st_pair_sys(uint2 *ptr, uint2 v) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(ptr), "r"(v.x), "r"(v.y) : "memory");
 }
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *ptr) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+__device__ __forceinline__ uint2 ld_pair_sys(const uint2 *ptr) {
+    uint2 v;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(ptr) : "memory");
     return v;
 }
 constexpr long long kExchangeWaitCycles = 2000000000LL;  // about a second; then the kernel reports QF_ERR_TIMEOUT
@@ -116,10 +116,10 @@ __device__ __forceinline__ ZeroScale<BF16> consts_from(const uint2 e) {
 // MPAD: rows of X staged per batch tile (1, 2, 4 or 8), a compile-time constant so that the activation
 // addressing in the main loop folds into immediates.
 // AR: this GPU holds a K shard of the weights (row-parallel linear). The block that finishes a column block
-// pushes its 64 x M fp32 partial outputs into every rank's slot with peer stores, raises a per-(column block,
-// source) counter on every rank, waits (bounded) until all ranks' pushes for the same column block have arrived
-// here, sums the slots in rank order (same bits on every rank) and writes Y. The exchange of a column block
-// overlaps the weight streams of the blocks still running; no separate all-reduce kernel follows.
+// pushes its 64 x M fp32 partial outputs into every rank's slot with peer stores, each value paired with the
+// call's token in one 8-byte store, then polls (bounded) its own slots until every rank's pair for the same
+// element carries that token, sums in rank order (same bits on every rank) and writes Y. The exchange of a
+// column block overlaps the weight streams of the blocks still running; no separate all-reduce kernel follows.
 // A waiting block depends only on blocks that the peers dispatched before their own waiting blocks (blocks are
 // dispatched in index order and a block waits only after every block of its column has arrived), so waiters
 // cannot starve the work they wait for; the wait is bounded all the same.
@@ -179,6 +179,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams 
     // Everything above is independent of the previous kernel in the stream; the activations are not.
     griddep_launch_dependents();
     griddep_wait();
+    unsigned ar_epoch = 0;
+    if constexpr (AR) ar_epoch = *(volatile const unsigned *)p.ar.epoch;
 
     // 3. activations of this K range in fragment order, zero rows beyond M
     {
@@ -320,58 +322,63 @@ __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams 
 
     if constexpr (AR) {
         const ArParams &ar = p.ar;
-        const int cb = blockIdx.z * gridDim.x + blockIdx.x;
-        const unsigned c = ar.seen[cb];  // calls this column block has completed on this comm (same on every rank)
-        const size_t par_off = (size_t)(c & 1u) * (size_t)ar.world * ar.slot_elems;
+        // `epoch` counts the calls completed on this comm (same value on every rank); it was read after the
+        // dependency wait, i.e. after the previous call on this rank had finished and advanced it.
+        const unsigned token = ar_epoch + 1u;
+        const size_t par_off = (size_t)(ar_epoch & 1u) * (size_t)ar.world * ar.slot_elems;
         if (tid == 0) s_ar_fail = 0;
-        // 1. push this rank's partial outputs into slot [parity][rank] of every rank (own included)
+        __syncthreads();
+        // 1. push (value, token) pairs into slot [parity][rank] of every rank, own included. One 8-byte store
+        //    carries the value and the token that says it is there, so no fence or separate flag is needed.
         for (int u = tid; u < GEMV_ROWS_PER_BLOCK * m_rows; u += GEMV_THREADS) {
             const int nl = u & (GEMV_ROWS_PER_BLOCK - 1);
             const int64_t n = n_blk + nl;
             const int64_t mm = (int64_t)mt * 8 + u / GEMV_ROWS_PER_BLOCK;
             if (n < p.N && mm < p.M) {
-                const float v = s_tile[u];
+                const uint2 pair = make_uint2(__float_as_uint(s_tile[u]), token);
                 const size_t off = par_off + (size_t)ar.rank * ar.slot_elems + (size_t)(mm * p.N + n);
-                for (int r = 0; r < ar.world; ++r) __stcg(ar.slots[r] + off, v);
+                for (int r = 0; r < ar.world; ++r) st_pair_sys(ar.slots[r] + off, pair);
             }
         }
-        __threadfence_system();
-        __syncthreads();
-        // 2. tell every rank; 3. wait for every rank's push of this column block
-        if (tid < ar.world) {
-            red_add_release_sys(ar.flags[tid] + (size_t)cb * kMaxPeers + ar.rank, 1u);
-            const unsigned *f = ar.flags[ar.rank] + (size_t)cb * kMaxPeers + tid;
-            const long long t0 = clock64();
-            while ((int)(ld_acquire_sys(f) - (c + 1u)) < 0) {
-                __nanosleep(100);
-                if (clock64() - t0 > kExchangeWaitCycles) {
-                    s_ar_fail = 1;
-                    break;
-                }
-            }
-        }
-        __syncthreads();
-        if (s_ar_fail) {
-            if (tid == 0) atomicExch(ar.status, QF_ERR_TIMEOUT);
-            return;
-        }
-        // 4. sum the slots in rank order and write the output
+        // 2. collect the pairs of every rank for the same elements, sum in rank order, write the output
         for (int u = tid; u < GEMV_ROWS_PER_BLOCK * m_rows; u += GEMV_THREADS) {
             const int nl = u & (GEMV_ROWS_PER_BLOCK - 1);
             const int64_t n = n_blk + nl;
             const int64_t mm = (int64_t)mt * 8 + u / GEMV_ROWS_PER_BLOCK;
             if (n < p.N && mm < p.M) {
-                const float *src = ar.slots[ar.rank] + par_off + (size_t)(mm * p.N + n);
-                float v[kMaxPeers];
-#pragma unroll
-                for (int r = 0; r < kMaxPeers; ++r) v[r] = (r < ar.world) ? __ldcg(src + (size_t)r * ar.slot_elems) : 0.f;
-                float s = 0.f;
-#pragma unroll
-                for (int r = 0; r < kMaxPeers; ++r) s += v[r];
-                store_out(p.Y, p.out_dtype, mm * p.N + n, s);
+                const uint2 *src = ar.slots[ar.rank] + par_off + (size_t)(mm * p.N + n);
+                float sum = 0.f;
+                bool ok = true;
+                const long long t0 = clock64();
+                for (int r = 0; r < ar.world && ok; ++r) {
+                    uint2 pair = ld_pair_sys(src + (size_t)r * ar.slot_elems);
+                    while (pair.y != token) {
+                        __nanosleep(40);
+                        if (clock64() - t0 > kExchangeWaitCycles || *(volatile int *)&s_ar_fail) {
+                            ok = false;
+                            break;
+                        }
+                        pair = ld_pair_sys(src + (size_t)r * ar.slot_elems);
+                    }
+                    sum += __uint_as_float(pair.x);
+                }
+                if (ok) store_out(p.Y, p.out_dtype, mm * p.N + n, sum);
+                else s_ar_fail = 1;
             }
         }
-        if (tid == 0) ar.seen[cb] = c + 1u;
+        __syncthreads();
+        if (tid == 0) {
+            if (s_ar_fail) atomicExch(ar.status, QF_ERR_TIMEOUT);
+            // the last column block of the launch to finish advances the epoch for the next call
+            const unsigned nblk = gridDim.x * gridDim.z;
+            __threadfence();
+            if (atomicAdd(ar.done, 1u) == nblk - 1u) {
+                *ar.done = 0u;
+                unsigned next = ar_epoch + 1u;
+                if (next == 0xFFFFFFFFu) next = 1u;  // its token would be 0, the value of never-written memory
+                *ar.epoch = next;
+            }
+        }
     }
 }
 
