@@ -260,6 +260,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1, help="batch rows for the stack workloads")
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers of a stack workload")
     ap.add_argument("--fuse", action="store_true", help="stack workloads: one launch for q/k/v and one for gate/up")
+    ap.add_argument("--nccl-collectives", action="store_true",
+                    help="sweep on N > 1 GPUs: follow each linear with an NCCL all-gather instead of gathering in-kernel")
     ap.add_argument("--fused-allreduce", action="store_true",
                     help="stack workloads on N > 1 GPUs, batch <= 8: row-parallel linears sum over ranks inside the kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -321,7 +323,17 @@ def main():
                           "x_host": x.cpu().pin_memory(), "y_host": torch.empty(M, Nl, dtype=torch.bfloat16).pin_memory()})
     total_bytes = sum(algo_bytes(c["M"], c["K"], c["N"]) for c in cases)  # whole job, all ranks
 
+    # N > 1: the gather of the column shards happens inside the linear kernels over NVLink peer memory
+    # (--nccl-collectives: the linear followed by an NCCL all-gather instead)
+    comm = None
+    if world > 1 and not args.nccl_collectives:
+        comm = qf.Comm(max(SWEEP_MS) * max(N for (_, N) in SWEEP_SHAPES) // world, device=dev)
+
     def launch(c):
+        if comm is not None:
+            qf.w4a16_linear_allgather(c["x"], c["qw"], c["sc"], c["zr"], comm, group_size=GROUP,
+                                      out=c["yg"].view(c["M"], world * c["Nl"]), weight_layout=c["layout"])
+            return
         qf.w4a16_linear(c["x"], c["qw"], c["sc"], c["zr"], group_size=GROUP, out=c["y"], weight_layout=c["layout"])
         if world > 1:
             dist.all_gather_into_tensor(c["yg"], c["y"])
@@ -526,7 +538,9 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "cfg1_sweep", "cases": "M in {1,4,8,16,64} x (K,N) in {(4096,4096),(4096,14336),(14336,4096)}",
                        "group_size": GROUP, "zeros": "uint4 per (group,n)", "out_dtype": "bf16",
-                       "parallelism": "single GPU" if world == 1 else f"column-parallel x{world} + NCCL all-gather",
+                       "parallelism": "single GPU" if world == 1 else
+                       (f"column-parallel x{world}, outputs gathered inside the kernels over NVLink peer memory"
+                        if comm is not None else f"column-parallel x{world} + NCCL all-gather"),
                        "l2": "inputs larger than L2: 15 weight copies, 335 MB touched per step",
                        "timing": "CUDA graph of one step replayed K times between CUDA events",
                        "clock_sampling": "timed region plus 1.5 s of the identical replay load"},
@@ -545,6 +559,8 @@ def main():
         gc.collect()
         torch.cuda.synchronize()
         dist.barrier()
+        if comm is not None:
+            comm.close()
         dist.destroy_process_group()
 
 

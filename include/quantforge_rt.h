@@ -186,16 +186,23 @@ int qf_w4a16_gemv_static_scratch(qf_ctx *ctx, const qf_linear_desc *desc, const 
                                  const void *scales, const void *qzeros_or_null, void *Y, void *stream);
 
 /*
- * Row-parallel linear with the cross-GPU sum inside the kernel. (No counterpart in the reference, which runs on
- * one device; the multi-GPU deployment this runtime adds would otherwise follow the linear with an NCCL all-reduce.)
+ * Tensor-parallel linears with the cross-GPU step inside the kernel. (No counterpart in the reference, which runs
+ * on one device; the multi-GPU deployment this runtime adds would otherwise follow each linear with an NCCL
+ * all-reduce or all-gather.) One process per GPU of one node, up to 8 ranks.
  *
- * Each rank (one process per GPU of one node) holds the K shard [rank*K/world, (rank+1)*K/world) of the weights,
- * scales and zeros and the matching columns of X; `desc->K` is the shard's K. Every rank receives the full sum in
- * its own Y, bit-identical on all ranks (fp32 partial outputs are summed in rank order, then rounded once).
- * The GEMV kernel (desc->M <= 8, canonical weights) pushes each finished block of 64 output columns into all
- * ranks' exchange buffers with peer stores over NVLink (value and arrival token in one 8-byte store) and polls
- * for the other ranks' pushes of the same block, so the exchange overlaps the weight streams still running and
- * no separate collective is launched.
+ * qf_w4a16_linear_allreduce  row-parallel: each rank holds the K shard [rank*K/world, (rank+1)*K/world) of the
+ *   weights, scales and zeros and the matching columns of X; `desc->K` is the shard's K. Every rank receives
+ *   the full sum in its own Y[M, N], bit-identical on all ranks (fp32 partial outputs summed in rank order,
+ *   then rounded once).
+ * qf_w4a16_linear_allgather  column-parallel: each rank holds the output-column shard [rank*N, (rank+1)*N) of the
+ *   weights (`desc->N` is the shard's N, the same on every rank) and the whole X. Every rank receives the whole
+ *   output in its own Y[M, world*N]; columns [r*N, (r+1)*N) come from rank r.
+ *
+ * Both serve desc->M <= 64 (decode batches; beyond that the exchange is bandwidth-bound on the links and a bulk
+ * collective after qf_w4a16_linear is the better tool) on either kernel, as qf_w4a16_linear would choose it.
+ * The block that finishes a tile of the output pushes it into all ranks' exchange buffers with peer stores over
+ * NVLink (value and arrival token in one 8-byte store) and polls for the other ranks' pushes of the same tile,
+ * so the exchange overlaps the weight streams still running and no separate collective is launched.
  *
  * Set-up, once per group of ranks:
  *   qf_comm_create(ctx, rank, world, max_out_elems, &comm)   allocates this rank's exchange buffer
@@ -204,10 +211,12 @@ int qf_w4a16_gemv_static_scratch(qf_ctx *ctx, const qf_linear_desc *desc, const 
  *   qf_comm_connect(comm, handles, world)                    handles of all ranks, in rank order; maps the peers
  *   <a barrier of the caller's own, e.g. torch.distributed.barrier()>  before the first call
  * and a barrier again before qf_comm_destroy. world == 1 needs no handles (connect may be skipped).
- * Rules: all ranks make the same sequence of calls on a comm (any mix of shapes); calls on one comm are stream-ordered on each rank
- * (one stream, or serialised); desc->M * desc->N <= max_out_elems. A rank that waits longer than about a second
- * for a peer gives up: its Y is not written, qf_ctx_status(ctx) reads QF_ERR_TIMEOUT after the stream is
- * synchronised, and the comm must be destroyed. `workspace` as for qf_w4a16_linear with desc->path = QF_PATH_GEMV.
+ * Rules: all ranks make the same sequence of calls on a comm (any mix of shapes and of the two entry points);
+ * calls on one comm are stream-ordered on each rank (one stream, or serialised); desc->M * desc->N <=
+ * max_out_elems. A rank that waits longer than about a second for a peer gives up: its Y is incomplete,
+ * qf_ctx_status(ctx) reads QF_ERR_TIMEOUT after the stream is synchronised, and the comm must be destroyed.
+ * `workspace` as for qf_w4a16_linear with the same desc. After 2^32 - 2 calls on one comm the arrival token
+ * repeats; an element that no call has written for that long could then be taken for arrived.
  */
 typedef struct qf_comm qf_comm;
 #define QF_COMM_HANDLE_BYTES 64
@@ -216,6 +225,9 @@ int qf_comm_export(const qf_comm *comm, void *handle_out);
 int qf_comm_connect(qf_comm *comm, const void *handles, int n_handles);
 int qf_comm_destroy(qf_comm *comm);
 int qf_w4a16_linear_allreduce(qf_ctx *ctx, qf_comm *comm, const qf_linear_desc *desc, const void *X,
+                              const void *qweight, const void *scales, const void *qzeros_or_null, void *Y,
+                              void *workspace, size_t workspace_bytes, void *stream);
+int qf_w4a16_linear_allgather(qf_ctx *ctx, qf_comm *comm, const qf_linear_desc *desc, const void *X,
                               const void *qweight, const void *scales, const void *qzeros_or_null, void *Y,
                               void *workspace, size_t workspace_bytes, void *stream);
 

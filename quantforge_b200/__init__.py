@@ -5,7 +5,7 @@ pack_int4, unpack_int4, gemv_int4_baseline) on top of the C ABI in include/quant
 """
 from .ops import (  # noqa: F401
     Comm, W4A16Linear, clear_device_status, dequant_w4, device_status, gemv_int4, launch_count, pack_int4, pack_zeros_u4,
-    prepack_w4, unpack_int4, w4a16_linear, w4a16_linear_allreduce, w4a16_linear_host, workspace_bytes,
+    prepack_w4, unpack_int4, w4a16_linear, w4a16_linear_allgather, w4a16_linear_allreduce, w4a16_linear_host, workspace_bytes,
 )
 from ._lib import (QF_LAYOUT_CANONICAL, QF_LAYOUT_INTERLEAVED, QF_LAYOUT_TILED, QF_PATH_AUTO, QF_PATH_GEMM,  # noqa: F401
                    QF_PATH_GEMV, QuantForgeError)

@@ -23,6 +23,7 @@ EXPORTS = [
     "qf_dequant_w4", "qf_w4a16_workspace_bytes", "qf_w4a16_linear", "qf_w4a16_linear_host", "qf_w4a16_plan",
     "qf_launch_count", "qf_prepack_w4", "qf_prepack_w4_tiled", "qf_w4a16_gemv_static_scratch", "qf_ctx_status", "qf_ctx_clear_status",
     "qf_comm_create", "qf_comm_export", "qf_comm_connect", "qf_comm_destroy", "qf_w4a16_linear_allreduce",
+    "qf_w4a16_linear_allgather",
 ]
 QF_COMM_HANDLE_BYTES = 64
 
@@ -83,6 +84,7 @@ def load() -> ctypes.CDLL:
     lib.qf_comm_connect.argtypes = [vp, vp, ctypes.c_int]
     lib.qf_comm_destroy.argtypes = [vp]
     lib.qf_w4a16_linear_allreduce.argtypes = [vp, vp, dp, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.qf_w4a16_linear_allgather.argtypes = [vp, vp, dp, vp, vp, vp, vp, vp, vp, sz, vp]
     _lib = lib
     return lib
 

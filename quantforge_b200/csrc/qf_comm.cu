@@ -23,6 +23,7 @@ namespace qf {
 static ArParams comm_params(const qf_comm *c) {
     ArParams ar = {};
     for (int r = 0; r < c->world; ++r) ar.slots[r] = (uint2 *)((char *)c->peer[r] + kCommHeaderBytes);
+    ar.local_slots = ar.slots[c->rank];
     ar.epoch = (unsigned *)c->local;
     ar.done = (unsigned *)c->local + 1;
     ar.status = c->ctx->dev_status;
@@ -109,40 +110,59 @@ int qf_comm_destroy(qf_comm *comm) {
     return QF_OK;
 }
 
-int qf_w4a16_linear_allreduce(qf_ctx *ctx, qf_comm *comm, const qf_linear_desc *desc, const void *X,
-                              const void *qweight, const void *scales, const void *qzeros_or_null, void *Y,
-                              void *workspace, size_t workspace_bytes, void *stream) {
+// Shared body of the two exchange entry points. The path follows the plan of qf_w4a16_linear (GEMV kernel for
+// M <= 2 or when N is not a multiple of 128, tcgen05 kernel otherwise) unless desc->path names one.
+static int linear_exchange(qf_ctx *ctx, qf_comm *comm, const qf_linear_desc *desc, const void *X,
+                           const void *qweight, const void *scales, const void *qzeros_or_null, void *Y,
+                           void *workspace, size_t workspace_bytes, void *stream, int gather) {
     if (!ctx) return QF_ERR_BAD_ARG;
     if (!comm || comm->ctx != ctx) return fail(ctx, QF_ERR_BAD_ARG, "comm is null or belongs to another context");
     if (!comm->connected) return fail(ctx, QF_ERR_BAD_ARG, "qf_comm_connect has not been called");
     if (!desc) return fail(ctx, QF_ERR_BAD_ARG, "desc is null");
-    qf_linear_desc d = *desc;
-    if (d.path == QF_PATH_GEMM || d.M > 8)
-        return fail(ctx, QF_ERR_UNSUPPORTED, "the fused cross-GPU sum exists in the GEMV kernel only (M <= 8)");
-    d.path = QF_PATH_GEMV;
-    if (d.weight_layout != QF_LAYOUT_CANONICAL)
-        return fail(ctx, QF_ERR_UNSUPPORTED, "the GEMV kernel reads canonical weights only");
+    if (desc->M > 64)
+        return fail(ctx, QF_ERR_UNSUPPORTED,
+                    "the in-kernel exchange serves M <= 64; larger batches are bandwidth-bound on the links and "
+                    "should follow the linear with a bulk collective");
     Plan plan;
     std::string why;
-    int st = make_plan(&d, &plan, &why);
+    int st = make_plan(desc, &plan, &why);
     if (st != QF_OK) return fail(ctx, st, why);
-    if (d.M == 0) return QF_OK;
+    if (desc->M == 0) return QF_OK;
     if (!X || !qweight || !scales || !Y) return fail(ctx, QF_ERR_BAD_ARG, "null tensor pointer");
-    if (d.zero_mode != QF_ZERO_CONST && !qzeros_or_null)
+    if (desc->zero_mode != QF_ZERO_CONST && !qzeros_or_null)
         return fail(ctx, QF_ERR_BAD_ARG, "zero_mode needs a qzeros tensor");
     auto al16 = [](const void *p) { return ((uintptr_t)p & 15u) == 0; };
     if (!al16(X) || !al16(qweight) || !al16(scales) || !al16(Y) || (qzeros_or_null && !al16(qzeros_or_null)))
         return fail(ctx, QF_ERR_BAD_ARG, "device pointers must be 16-byte aligned");
-    if ((size_t)d.M * (size_t)d.N > comm->slot_elems)
+    if ((size_t)desc->M * (size_t)desc->N > comm->slot_elems)
         return fail(ctx, QF_ERR_WORKSPACE, "M*N exceeds the max_out_elems this comm was created with");
     const size_t need = plan.ws_partial_bytes + plan.ws_counter_bytes;
     if (need > 0) {
         if (!workspace || workspace_bytes < need)
-            return fail(ctx, QF_ERR_WORKSPACE, "workspace smaller than qf_w4a16_workspace_bytes(desc, path = GEMV)");
+            return fail(ctx, QF_ERR_WORKSPACE, "workspace smaller than qf_w4a16_workspace_bytes(desc)");
         if (!al16(workspace)) return fail(ctx, QF_ERR_BAD_ARG, "workspace must be 16-byte aligned");
     }
-    const ArParams ar = comm_params(comm);
-    return launch_gemv_ar(ctx, &d, plan, X, qweight, scales, qzeros_or_null, Y, workspace, (cudaStream_t)stream, ar);
+    ArParams ar = comm_params(comm);
+    ar.gather = gather;
+    if (plan.path == QF_PATH_GEMV)
+        return launch_gemv_ar(ctx, desc, plan, X, qweight, scales, qzeros_or_null, Y, workspace,
+                              (cudaStream_t)stream, ar);
+    return launch_gemm_ar(ctx, desc, plan, X, qweight, scales, qzeros_or_null, Y, workspace, (cudaStream_t)stream,
+                          ar);
+}
+
+int qf_w4a16_linear_allreduce(qf_ctx *ctx, qf_comm *comm, const qf_linear_desc *desc, const void *X,
+                              const void *qweight, const void *scales, const void *qzeros_or_null, void *Y,
+                              void *workspace, size_t workspace_bytes, void *stream) {
+    return linear_exchange(ctx, comm, desc, X, qweight, scales, qzeros_or_null, Y, workspace, workspace_bytes, stream,
+                           0);
+}
+
+int qf_w4a16_linear_allgather(qf_ctx *ctx, qf_comm *comm, const qf_linear_desc *desc, const void *X,
+                              const void *qweight, const void *scales, const void *qzeros_or_null, void *Y,
+                              void *workspace, size_t workspace_bytes, void *stream) {
+    return linear_exchange(ctx, comm, desc, X, qweight, scales, qzeros_or_null, Y, workspace, workspace_bytes, stream,
+                           1);
 }
 
 }  // extern "C"

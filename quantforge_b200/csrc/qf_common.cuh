@@ -101,12 +101,14 @@ constexpr size_t kCommHeaderBytes = 256;  // epoch, done, padding
 // rank's pushes of call k+1, and a rank pushes for call k+1 only after its own call k (and its reads) finished.
 struct ArParams {
     uint2 *slots[kMaxPeers];      // slots region of every rank's buffer (own rank: local address)
+    uint2 *local_slots;           // = slots[rank]
     unsigned *epoch;              // local
     unsigned *done;               // local
     int *status;                  // device status word of the context (bounded waits report here)
     unsigned long long slot_elems;
     int world;
     int rank;
+    int gather;                   // 0: Y[M, N] = sum over ranks; 1: Y[M, world*N], columns [r*N, (r+1)*N) from rank r
 };
 
 // Validates `d` and fills the launch plan. Returns QF_OK or an error status; `why` receives a message.
@@ -125,6 +127,8 @@ int launch_prepack_tiled(qf_ctx *ctx, const void *in, void *out, int64_t N, int6
                          cudaStream_t s);
 int gemm_block_k(int bn);
 int launch_gemv_ar(qf_ctx *ctx, const qf_linear_desc *d, const Plan &p, const void *X, const void *qw,
+                   const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s, const ArParams &ar);
+int launch_gemm_ar(qf_ctx *ctx, const qf_linear_desc *d, const Plan &p, const void *X, const void *qw,
                    const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s, const ArParams &ar);
 int launch_gemv_static(qf_ctx *ctx, const qf_linear_desc *d, const Plan &p, const void *X, const void *qw,
                        const void *scales, const void *zeros, void *Y, cudaStream_t s);
@@ -249,6 +253,154 @@ __device__ __forceinline__ void store_out(void *Y, int out_dtype, int64_t idx, f
         reinterpret_cast<__half *>(Y)[idx] = __float2half_rn(v);
     } else {
         reinterpret_cast<__nv_bfloat16 *>(Y)[idx] = __float2bfloat16_rn(v);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Cross-GPU exchange of finished output elements (device side). An element is pushed as an 8-byte
+// (value, token) pair, written and read whole, so the pair itself says that it has arrived.
+// ---------------------------------------------------------------------------------------------
+constexpr long long kExchangeWaitCycles = 2000000000LL;  // about a second; then the kernel reports QF_ERR_TIMEOUT
+
+__device__ __forceinline__ void st_pair_sys(uint2 *ptr, uint2 v) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(ptr), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ uint2 ld_pair_sys(const uint2 *ptr) {
+    uint2 v;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(ptr) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned exch_read_epoch(const ArParams &ar) {
+    unsigned e;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(e) : "l"(ar.epoch) : "memory");
+    return e;
+}
+__device__ __forceinline__ size_t exch_parity_offset(const ArParams &ar, unsigned epoch) {
+    return (size_t)(epoch & 1u) * (size_t)ar.world * ar.slot_elems;
+}
+// Element `elem` (= m * N + n of this rank's output) of call `epoch` to every rank, own included.
+__device__ __forceinline__ void exch_push(const ArParams &ar, unsigned epoch, size_t elem, float v) {
+    const uint2 pair = make_uint2(__float_as_uint(v), epoch + 1u);
+    const size_t off = exch_parity_offset(ar, epoch) + (size_t)ar.rank * ar.slot_elems + elem;
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)  // unrolled: the pointer table stays in the kernel's parameter space
+        if (r < ar.world) st_pair_sys(ar.slots[r] + off, pair);
+}
+// Two neighbouring elements (even n) as one 16-byte store / load; each 8-byte half is still written whole.
+__device__ __forceinline__ void st_pair2_sys(uint2 *ptr, uint4 v) {
+    asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(ptr), "r"(v.x), "r"(v.y), "r"(v.z),
+                 "r"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ uint4 ld_pair2_sys(const uint2 *ptr) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(ptr)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ void exch_push2(const ArParams &ar, unsigned epoch, size_t elem, float v0, float v1) {
+    const uint4 pair2 = make_uint4(__float_as_uint(v0), epoch + 1u, __float_as_uint(v1), epoch + 1u);
+    const size_t off = exch_parity_offset(ar, epoch) + (size_t)ar.rank * ar.slot_elems + elem;
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+        if (r < ar.world) st_pair2_sys(ar.slots[r] + off, pair2);
+}
+// Collects the tile rows [m0, m0+mrows) x columns [n0, n0+ncols) (ncols even; clipped to M and N) from every
+// rank's slot and writes it out: the sum in rank order, or each rank's values into its own column range.
+// A load from the slots costs a full L2 round trip, so each thread keeps U two-element units x W ranks in flight
+// before it looks at any token, then polls (bounded) what has not arrived, again all at once. Returns false when a wait ran
+// out or another thread already gave up.
+template <int W, int U>
+__device__ __forceinline__ bool exch_collect_tile_impl(const ArParams &ar, unsigned epoch, int64_t m0, int mrows,
+                                                       int64_t n0, int ncols, int64_t M, int64_t N, void *Y,
+                                                       int out_dtype, int tid, int nthreads, volatile int *fail) {
+    const unsigned token = epoch + 1u;
+    const uint2 *base = ar.local_slots + exch_parity_offset(ar, epoch);
+    const int upr = ncols >> 1;  // 2-element units per row
+    const int total = mrows * upr;
+    const long long t0 = clock64();
+    for (int u0 = tid; u0 < total; u0 += U * nthreads) {
+        uint4 v[U][W];
+        int64_t mm[U], nn[U];
+        bool valid[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const int u = u0 + j * nthreads;
+            mm[j] = m0 + u / upr;
+            nn[j] = n0 + 2 * (u % upr);
+            valid[j] = u < total && mm[j] < M && nn[j] < N;
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j)
+#pragma unroll
+            for (int r = 0; r < W; ++r)
+                if (valid[j] && r < ar.world)
+                    v[j][r] = ld_pair2_sys(base + (size_t)r * ar.slot_elems + (size_t)(mm[j] * N + nn[j]));
+        // poll what has not arrived, all missing units at once (one round trip per round, not per unit)
+        while (true) {
+            bool miss = false;
+#pragma unroll
+            for (int j = 0; j < U; ++j)
+#pragma unroll
+                for (int r = 0; r < W; ++r)
+                    if (valid[j] && r < ar.world && (v[j][r].y != token || v[j][r].w != token)) miss = true;
+            if (!miss) break;
+            __nanosleep(100);
+            if (clock64() - t0 > kExchangeWaitCycles || *fail) return false;
+#pragma unroll
+            for (int j = 0; j < U; ++j)
+#pragma unroll
+                for (int r = 0; r < W; ++r)
+                    if (valid[j] && r < ar.world && (v[j][r].y != token || v[j][r].w != token))
+                        v[j][r] = ld_pair2_sys(base + (size_t)r * ar.slot_elems + (size_t)(mm[j] * N + nn[j]));
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            if (!valid[j]) continue;
+            if (ar.gather) {
+                const int64_t row = mm[j] * (N * ar.world) + nn[j];
+#pragma unroll
+                for (int r = 0; r < W; ++r)
+                    if (r < ar.world) {
+                        store_out(Y, out_dtype, row + (int64_t)r * N, __uint_as_float(v[j][r].x));
+                        store_out(Y, out_dtype, row + (int64_t)r * N + 1, __uint_as_float(v[j][r].z));
+                    }
+            } else {
+                float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+                for (int r = 0; r < W; ++r)
+                    if (r < ar.world) {
+                        s0 += __uint_as_float(v[j][r].x);
+                        s1 += __uint_as_float(v[j][r].z);
+                    }
+                store_out(Y, out_dtype, mm[j] * N + nn[j], s0);
+                store_out(Y, out_dtype, mm[j] * N + nn[j] + 1, s1);
+            }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ bool exch_collect_tile(const ArParams &ar, unsigned epoch, int64_t m0, int mrows, int64_t n0,
+                                                  int ncols, int64_t M, int64_t N, void *Y, int out_dtype, int tid,
+                                                  int nthreads, volatile int *fail) {
+    if (ar.world <= 2)
+        return exch_collect_tile_impl<2, 8>(ar, epoch, m0, mrows, n0, ncols, M, N, Y, out_dtype, tid, nthreads, fail);
+    if (ar.world <= 4)
+        return exch_collect_tile_impl<4, 4>(ar, epoch, m0, mrows, n0, ncols, M, N, Y, out_dtype, tid, nthreads, fail);
+    return exch_collect_tile_impl<8, 2>(ar, epoch, m0, mrows, n0, ncols, M, N, Y, out_dtype, tid, nthreads, fail);
+}
+// One thread per finished block, after the block's collects: the last block of the launch advances the epoch.
+__device__ __forceinline__ void exch_block_done(const ArParams &ar, unsigned epoch, unsigned blocks_in_launch,
+                                                bool failed) {
+    if (failed) atomicExch(ar.status, QF_ERR_TIMEOUT);
+    __threadfence();
+    if (atomicAdd(ar.done, 1u) == blocks_in_launch - 1u) {
+        *ar.done = 0u;
+        unsigned next = epoch + 1u;
+        if (next == 0xFFFFFFFFu) next = 1u;  // its token would be 0, the value of never-written memory
+        *ar.epoch = next;
     }
 }
 

@@ -67,6 +67,7 @@ struct GemmParams {
     int split_k;
     int interleaved;       // weight nibble order inside a word: 0 canonical, 1 pair-interleaved
     int tiled;             // 1: weights stored tile-major (QF_LAYOUT_TILED)
+    ArParams ar;           // ar.world > 0: finished tiles are exchanged across GPUs (sum or gather) before Y is written
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -243,6 +244,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
     constexpr int BK = C::BK;
     constexpr int STAGES = C::STAGES;
     constexpr int NA = C::NA;
+    constexpr bool EXCH = BN <= 64;  // the cross-GPU exchange serves decode batches only
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t s_tmem_base;
@@ -454,6 +456,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
         const bool ok = __all_sync(0xffffffffu, mbar_wait(dfull_bar, 0, abort_flag));
         tc_fence_after();
         if (ok) {
+            // the activations this tile consumed were requested after the dependency wait, so the previous call on
+            // this rank has finished and advanced the epoch
+            const unsigned ar_epoch = (EXCH && p.ar.world > 0 && p.split_k == 1) ? exch_read_epoch(p.ar) : 0u;
             constexpr int COLS_PER_WG = BN / 2;
             const int64_t Mp = (int64_t)gridDim.x * BN;
 #pragma unroll 1
@@ -467,7 +472,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                     const int64_t m = m0 + col + j;
                     const float v = __uint_as_float(r[j]);
                     if (p.split_k == 1) {
-                        if (m < p.M) store_out(p.Y, p.out_dtype, m * p.N + n, v);
+                        if (m < p.M) {
+                            if (EXCH && p.ar.world > 0) exch_push(p.ar, ar_epoch, (size_t)(m * p.N + n), v);
+                            else store_out(p.Y, p.out_dtype, m * p.N + n, v);
+                        }
                     } else {
                         __stcg(p.partial + ((int64_t)split * Mp + m) * p.N + n, v);
                     }
@@ -489,51 +497,71 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
         }
         if (tid == 0) atomicExch(p.status, QF_ERR_TIMEOUT);
         __syncthreads();
-    } else if (p.split_k > 1) {
-        // split-K: last CTA of this (m_tile, n_tile) sums the partial tiles in split order
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            int *cnt = p.counters + (int64_t)n_tile * gridDim.x + m_tile;
-            const int prev = atomicAdd(cnt, 1);
-            s_is_last = (prev == p.split_k - 1);
-            if (s_is_last) *cnt = 0;
-        }
-        __syncthreads();
-        if (s_is_last) {
+    } else {
+        bool final_cta = true;  // this CTA holds (or has pushed) the finished tile
+        const unsigned ar_epoch = (EXCH && p.ar.world > 0) ? exch_read_epoch(p.ar) : 0u;
+        if (p.split_k > 1) {
+            // split-K: last CTA of this (m_tile, n_tile) sums the partial tiles in split order
             __threadfence();
-            // Sum the partial tiles in split order. Each thread owns 4 consecutive output columns (one 16-byte load
-            // per split) and keeps 4 splits in flight, so the reduction is not a chain of dependent L2 round trips.
-            const int64_t Mp = (int64_t)gridDim.x * BN;
-            const size_t split_stride = (size_t)Mp * p.N;
-            for (int u = tid; u < 32 * BN; u += GEMM_THREADS) {
-                const int nl = (u & 31) * 4;
-                const int64_t m = m0 + (u >> 5);
-                if (m < p.M) {
-                    const float *base = p.partial + (size_t)m * p.N + n0 + nl;
-                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int sp0 = 0; sp0 < p.split_k; sp0 += 4) {
-                        float4 v[4];
+            __syncthreads();
+            if (tid == 0) {
+                int *cnt = p.counters + (int64_t)n_tile * gridDim.x + m_tile;
+                const int prev = atomicAdd(cnt, 1);
+                s_is_last = (prev == p.split_k - 1);
+                if (s_is_last) *cnt = 0;
+            }
+            __syncthreads();
+            final_cta = s_is_last != 0;
+            if (final_cta) {
+                __threadfence();
+                // Each thread owns 4 consecutive output columns (one 16-byte load per split) and keeps 4 splits in
+                // flight, so the reduction is not a chain of dependent L2 round trips.
+                const int64_t Mp = (int64_t)gridDim.x * BN;
+                const size_t split_stride = (size_t)Mp * p.N;
+                for (int u = tid; u < 32 * BN; u += GEMM_THREADS) {
+                    const int nl = (u & 31) * 4;
+                    const int64_t m = m0 + (u >> 5);
+                    if (m < p.M) {
+                        const float *base = p.partial + (size_t)m * p.N + n0 + nl;
+                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (int sp0 = 0; sp0 < p.split_k; sp0 += 4) {
+                            float4 v[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            v[j] = (sp0 + j < p.split_k)
-                                       ? __ldcg(reinterpret_cast<const float4 *>(base + (size_t)(sp0 + j) * split_stride))
-                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+                            for (int j = 0; j < 4; ++j)
+                                v[j] = (sp0 + j < p.split_k)
+                                           ? __ldcg(reinterpret_cast<const float4 *>(base + (size_t)(sp0 + j) * split_stride))
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            acc.x += v[j].x;
-                            acc.y += v[j].y;
-                            acc.z += v[j].z;
-                            acc.w += v[j].w;
+                            for (int j = 0; j < 4; ++j) {
+                                acc.x += v[j].x;
+                                acc.y += v[j].y;
+                                acc.z += v[j].z;
+                                acc.w += v[j].w;
+                            }
+                        }
+                        const int64_t o = m * p.N + n0 + nl;
+                        if (EXCH && p.ar.world > 0) {
+                            exch_push2(p.ar, ar_epoch, (size_t)o, acc.x, acc.y);
+                            exch_push2(p.ar, ar_epoch, (size_t)o + 2, acc.z, acc.w);
+                        } else {
+                            store_out(p.Y, p.out_dtype, o, acc.x);
+                            store_out(p.Y, p.out_dtype, o + 1, acc.y);
+                            store_out(p.Y, p.out_dtype, o + 2, acc.z);
+                            store_out(p.Y, p.out_dtype, o + 3, acc.w);
                         }
                     }
-                    const int64_t o = m * p.N + n0 + nl;
-                    store_out(p.Y, p.out_dtype, o, acc.x);
-                    store_out(p.Y, p.out_dtype, o + 1, acc.y);
-                    store_out(p.Y, p.out_dtype, o + 2, acc.z);
-                    store_out(p.Y, p.out_dtype, o + 3, acc.w);
                 }
             }
+        }
+        if (EXCH && p.ar.world > 0 && final_cta) {
+            // Cross-GPU step: every element of the tile has been pushed to all ranks (above, or in the epilogue);
+            // collect the other ranks' values for the same elements and write the output. The pairs carry their
+            // own arrival token, so no block-level synchronisation separates the pushes from the collects.
+            if (!exch_collect_tile(p.ar, ar_epoch, m0, BN, n0, 128, p.M, p.N, p.Y, p.out_dtype, tid, GEMM_THREADS,
+                                   abort_flag))
+                s_abort = 1;
+            __syncthreads();
+            if (tid == 0) exch_block_done(p.ar, ar_epoch, gridDim.x * gridDim.y, s_abort != 0);
         }
     }
     if (warp == 9) {
@@ -681,9 +709,11 @@ static int gemm_launch_dt(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan
 
 int gemm_block_k(int bn) { return bn <= 128 ? 128 : 64; }
 
-int launch_gemm(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
-                const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s) {
+static int launch_gemm_impl(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
+                            const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s,
+                            const ArParams *ar) {
     GemmParams p;
+    p.ar = ar ? *ar : ArParams{};
     p.scales = (const uint16_t *)scales;
     p.zeros = zeros;
     p.Y = Y;
@@ -702,6 +732,16 @@ int launch_gemm(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const vo
     p.tiled = d->weight_layout == QF_LAYOUT_TILED;
     if (d->act_dtype == QF_BF16) return gemm_launch_dt<true>(ctx, d, plan, X, qw, p, s);
     return gemm_launch_dt<false>(ctx, d, plan, X, qw, p, s);
+}
+
+int launch_gemm(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
+                const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s) {
+    return launch_gemm_impl(ctx, d, plan, X, qw, scales, zeros, Y, ws, s, nullptr);
+}
+
+int launch_gemm_ar(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
+                   const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s, const ArParams &ar) {
+    return launch_gemm_impl(ctx, d, plan, X, qw, scales, zeros, Y, ws, s, &ar);
 }
 
 }  // namespace qf

@@ -50,17 +50,6 @@ struct GemvParams {
     ArParams ar;        // read by the AR (cross-GPU sum) instantiations only
 };
 
-// cross-GPU exchange: 8-byte (value, token) pairs, written and read whole
-__device__ __forceinline__ void st_pair_sys(uint2 *ptr, uint2 v) {
-    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(ptr), "r"(v.x), "r"(v.y) : "memory");
-}
-__device__ __forceinline__ uint2 ld_pair_sys(const uint2 *ptr) {
-    uint2 v;
-    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(ptr) : "memory");
-    return v;
-}
-constexpr long long kExchangeWaitCycles = 2000000000LL;  // about a second; then the kernel reports QF_ERR_TIMEOUT
-
 // dynamic shared memory: ring | constants table [chunks][64 rows] uint2 | staged X [chunks][4][m_pad][4] uint4
 static inline size_t gemv_smem_bytes(int chunks_per_split, int m_pad) {
     return (size_t)GEMV_RING_BYTES + (size_t)chunks_per_split * GEMV_ROWS_PER_BLOCK * 8 +
@@ -127,7 +116,7 @@ template <bool BF16, int ZMODE, int MPAD, bool AR = false>
 __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __shared__ int s_is_last;
-    __shared__ int s_ar_fail;
+    __shared__ volatile int s_ar_fail;
     __shared__ float s_tile[AR ? 8 * GEMV_ROWS_PER_BLOCK : 1];  // [batch row][column] of the finished column block
 
     const int tid = threadIdx.x;
@@ -180,7 +169,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams 
     griddep_launch_dependents();
     griddep_wait();
     unsigned ar_epoch = 0;
-    if constexpr (AR) ar_epoch = *(volatile const unsigned *)p.ar.epoch;
+    if constexpr (AR) ar_epoch = exch_read_epoch(p.ar);
 
     // 3. activations of this K range in fragment order, zero rows beyond M
     {
@@ -322,63 +311,26 @@ __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams 
 
     if constexpr (AR) {
         const ArParams &ar = p.ar;
-        // `epoch` counts the calls completed on this comm (same value on every rank); it was read after the
+        // ar_epoch counts the calls completed on this comm (same value on every rank); it was read after the
         // dependency wait, i.e. after the previous call on this rank had finished and advanced it.
-        const unsigned token = ar_epoch + 1u;
-        const size_t par_off = (size_t)(ar_epoch & 1u) * (size_t)ar.world * ar.slot_elems;
         if (tid == 0) s_ar_fail = 0;
         __syncthreads();
-        // 1. push (value, token) pairs into slot [parity][rank] of every rank, own included. One 8-byte store
-        //    carries the value and the token that says it is there, so no fence or separate flag is needed.
-        for (int u = tid; u < GEMV_ROWS_PER_BLOCK * m_rows; u += GEMV_THREADS) {
-            const int nl = u & (GEMV_ROWS_PER_BLOCK - 1);
+        // 1. push this block's elements to every rank, two neighbouring columns per 16-byte store
+        for (int u = tid; u < (GEMV_ROWS_PER_BLOCK / 2) * m_rows; u += GEMV_THREADS) {
+            const int nl = 2 * (u & (GEMV_ROWS_PER_BLOCK / 2 - 1));
+            const int m = u / (GEMV_ROWS_PER_BLOCK / 2);
             const int64_t n = n_blk + nl;
-            const int64_t mm = (int64_t)mt * 8 + u / GEMV_ROWS_PER_BLOCK;
-            if (n < p.N && mm < p.M) {
-                const uint2 pair = make_uint2(__float_as_uint(s_tile[u]), token);
-                const size_t off = par_off + (size_t)ar.rank * ar.slot_elems + (size_t)(mm * p.N + n);
-                for (int r = 0; r < ar.world; ++r) st_pair_sys(ar.slots[r] + off, pair);
-            }
+            const int64_t mm = (int64_t)mt * 8 + m;
+            if (n < p.N && mm < p.M)
+                exch_push2(ar, ar_epoch, (size_t)(mm * p.N + n), s_tile[m * GEMV_ROWS_PER_BLOCK + nl],
+                           s_tile[m * GEMV_ROWS_PER_BLOCK + nl + 1]);
         }
-        // 2. collect the pairs of every rank for the same elements, sum in rank order, write the output
-        for (int u = tid; u < GEMV_ROWS_PER_BLOCK * m_rows; u += GEMV_THREADS) {
-            const int nl = u & (GEMV_ROWS_PER_BLOCK - 1);
-            const int64_t n = n_blk + nl;
-            const int64_t mm = (int64_t)mt * 8 + u / GEMV_ROWS_PER_BLOCK;
-            if (n < p.N && mm < p.M) {
-                const uint2 *src = ar.slots[ar.rank] + par_off + (size_t)(mm * p.N + n);
-                float sum = 0.f;
-                bool ok = true;
-                const long long t0 = clock64();
-                for (int r = 0; r < ar.world && ok; ++r) {
-                    uint2 pair = ld_pair_sys(src + (size_t)r * ar.slot_elems);
-                    while (pair.y != token) {
-                        __nanosleep(40);
-                        if (clock64() - t0 > kExchangeWaitCycles || *(volatile int *)&s_ar_fail) {
-                            ok = false;
-                            break;
-                        }
-                        pair = ld_pair_sys(src + (size_t)r * ar.slot_elems);
-                    }
-                    sum += __uint_as_float(pair.x);
-                }
-                if (ok) store_out(p.Y, p.out_dtype, mm * p.N + n, sum);
-                else s_ar_fail = 1;
-            }
-        }
+        // 2. collect every rank's pairs for the same elements and write the output
+        if (!exch_collect_tile(ar, ar_epoch, (int64_t)mt * 8, m_rows, n_blk, GEMV_ROWS_PER_BLOCK, p.M, p.N, p.Y,
+                               p.out_dtype, tid, GEMV_THREADS, &s_ar_fail))
+            s_ar_fail = 1;
         __syncthreads();
-        if (tid == 0) {
-            if (s_ar_fail) atomicExch(ar.status, QF_ERR_TIMEOUT);
-            // the last column block of the launch to finish advances the epoch for the next call
-            const unsigned nblk = gridDim.x * gridDim.z;
-            __threadfence();
-            if (atomicAdd(ar.done, 1u) == nblk - 1u) {
-                *ar.done = 0u;
-                unsigned next = ar_epoch + 1u;
-                if (next == 0xFFFFFFFFu) next = 1u;  // its token would be 0, the value of never-written memory
-                *ar.epoch = next;
-            }
-        }
+        if (tid == 0) exch_block_done(ar, ar_epoch, gridDim.x * gridDim.z, s_ar_fail != 0);
     }
 }
 

@@ -256,31 +256,49 @@ class Comm:
             self._h = ctypes.c_void_p()
 
 
-def w4a16_linear_allreduce(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
-                           zeros: Optional[torch.Tensor], comm: Comm, group_size: int = 128, zero_const: int = 8,
-                           out_dtype: Optional[torch.dtype] = None, split_k: int = 0,
-                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Row-parallel linear: this rank's K shard of X and of the weights in, the sum over all ranks out (on every
-    rank, bit-identical), summed inside the GEMV kernel over NVLink peer memory. M <= 8, canonical weights."""
+def _linear_exchange(fn_name, gather, x, qweight, scales, zeros, comm, group_size, zero_const, out_dtype, path,
+                     split_k, out, weight_layout):
     dev = _need_cuda(x, qweight, scales, zeros)
     M, N, K = _check_linear_tensors(x, qweight, scales, zeros, group_size)
     out_dtype = out_dtype or x.dtype
     x, qweight, scales = x.contiguous(), qweight.contiguous(), scales.contiguous()
     zeros = zeros.contiguous() if zeros is not None else None
+    shape = (M, N * comm.world) if gather else (M, N)
     if out is None:
-        out = torch.empty((M, N), dtype=out_dtype, device=dev)
-    elif tuple(out.shape) != (M, N) or out.dtype != out_dtype or not out.is_contiguous():
-        raise ValueError("out must be a contiguous [M, N] tensor of out_dtype")
-    d = _make_desc(M, N, K, group_size, x.dtype, out_dtype, zeros, zero_const, QF_PATH_GEMV, split_k,
-                   QF_LAYOUT_CANONICAL)
+        out = torch.empty(shape, dtype=out_dtype, device=dev)
+    elif tuple(out.shape) != shape or out.dtype != out_dtype or not out.is_contiguous():
+        raise ValueError(f"out must be a contiguous {list(shape)} tensor of out_dtype")
+    d = _make_desc(M, N, K, group_size, x.dtype, out_dtype, zeros, zero_const, path, split_k, weight_layout)
     ctx = _ctx(dev)
     with torch.cuda.device(dev):
         ws = _workspace(dev, workspace_bytes(d))
-        st = _lib.load().qf_w4a16_linear_allreduce(ctx, comm._h, ctypes.byref(d), _ptr(x), _ptr(qweight),
-                                                   _ptr(scales), _ptr(zeros), _ptr(out), _ptr(ws),
-                                                   ws.numel() if ws is not None else 0, _stream(dev))
+        st = getattr(_lib.load(), fn_name)(ctx, comm._h, ctypes.byref(d), _ptr(x), _ptr(qweight), _ptr(scales),
+                                           _ptr(zeros), _ptr(out), _ptr(ws), ws.numel() if ws is not None else 0,
+                                           _stream(dev))
     _check(st, ctx)
     return out
+
+
+def w4a16_linear_allreduce(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
+                           zeros: Optional[torch.Tensor], comm: Comm, group_size: int = 128, zero_const: int = 8,
+                           out_dtype: Optional[torch.dtype] = None, split_k: int = 0,
+                           out: Optional[torch.Tensor] = None, path: int = QF_PATH_AUTO,
+                           weight_layout: int = QF_LAYOUT_CANONICAL) -> torch.Tensor:
+    """Row-parallel linear: this rank's K shard of X and of the weights in, the sum over all ranks out (on every
+    rank, bit-identical), summed inside the kernel over NVLink peer memory. M <= 64."""
+    return _linear_exchange("qf_w4a16_linear_allreduce", False, x, qweight, scales, zeros, comm, group_size,
+                            zero_const, out_dtype, path, split_k, out, weight_layout)
+
+
+def w4a16_linear_allgather(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
+                           zeros: Optional[torch.Tensor], comm: Comm, group_size: int = 128, zero_const: int = 8,
+                           out_dtype: Optional[torch.dtype] = None, split_k: int = 0,
+                           out: Optional[torch.Tensor] = None, path: int = QF_PATH_AUTO,
+                           weight_layout: int = QF_LAYOUT_CANONICAL) -> torch.Tensor:
+    """Column-parallel linear: the whole X and this rank's shard of output columns in, Y[M, world*N_local] out on
+    every rank (columns [r*N_local, (r+1)*N_local) from rank r), gathered inside the kernel. M <= 64."""
+    return _linear_exchange("qf_w4a16_linear_allgather", True, x, qweight, scales, zeros, comm, group_size,
+                            zero_const, out_dtype, path, split_k, out, weight_layout)
 
 
 def w4a16_linear_host(x_host: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,

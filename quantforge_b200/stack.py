@@ -44,8 +44,8 @@ class DecodeLinearStack:
                  fuse: bool = False, fused_allreduce: bool = False):
         """fuse=True runs q/k/v as ONE linear over the concatenated output rows and gate/up likewise (4 launches
         per layer instead of 7; same weights, same bytes, same results).
-        fused_allreduce=True (world > 1, batch <= 8): the row-parallel o and down linears sum across ranks inside
-        the GEMV kernel over peer memory instead of being followed by an NCCL all-reduce."""
+        fused_allreduce=True (world > 1, batch <= 64): the row-parallel o and down linears sum across ranks inside
+        the kernel over peer memory instead of being followed by an NCCL all-reduce."""
         self.cfg, self.M, self.dtype = cfg, batch, dtype
         self.dev = device or torch.device("cuda", torch.cuda.current_device())
         self.world, self.rank, self.group = world, rank, group
@@ -58,10 +58,10 @@ class DecodeLinearStack:
         self.fuse = fuse
         self.comm = None
         if fused_allreduce and world > 1:
-            if batch > 8:
-                raise ValueError("fused_allreduce needs batch <= 8 (GEMV kernel)")
+            if batch > 64:
+                raise ValueError("fused_allreduce needs batch <= 64")
             self.comm = ops.Comm(batch * H, device=self.dev, group=group)
-        prepack_row = prepack and self.comm is None  # the GEMV kernel reads canonical weights
+        prepack_row = prepack
         self.layers = []
         for _ in range(self.L):
             if fuse:
@@ -104,7 +104,8 @@ class DecodeLinearStack:
     def _row(self, w, x, out):
         """Row-parallel linear + sum over ranks."""
         if self.comm is not None:
-            ops.w4a16_linear_allreduce(x, w["qw"], w["sc"], w["zr"], self.comm, group_size=GROUP, out=out)
+            ops.w4a16_linear_allreduce(x, w["qw"], w["sc"], w["zr"], self.comm, group_size=GROUP, out=out,
+                                       weight_layout=w["layout"])
             return
         self._lin(w, x, out)
         if self.world > 1:

@@ -61,11 +61,16 @@ def shard_row(qweight, scales, zeros, rank: int, world: int):
 
 
 class ColumnParallelLinear:
-    """y_r = x . W[N_r, :]^T ; gather_output=True all-gathers into [M, N]."""
+    """y_r = x . W[N_r, :]^T ; gather_output=True all-gathers into [M, N].
+
+    With `comm` (an `ops.Comm` of the same ranks), gather_output and M <= 64 the gather happens inside the kernel
+    over NVLink peer memory and no NCCL collective is issued.
+    """
 
     def __init__(self, qweight, scales, zeros=None, group_size: int = 128, zero_const: int = 8,
                  group: Optional[dist.ProcessGroup] = None, gather_output: bool = True,
-                 compute: Optional[Callable] = None, prepack: bool = False):
+                 compute: Optional[Callable] = None, prepack: bool = False, comm: Optional["ops.Comm"] = None):
+        self.comm = comm
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -87,6 +92,10 @@ class ColumnParallelLinear:
                                 weight_layout=self.weight_layout)
 
     def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        if (self.comm is not None and self.compute is None and self.gather_output and self.world > 1 and
+                x.shape[0] <= 64):
+            return ops.w4a16_linear_allgather(x, self.qweight, self.scales, self.zeros, self.comm, self.group_size,
+                                              self.zero_const, out_dtype, weight_layout=self.weight_layout)
         y = self._local(x, out_dtype)
         if not self.gather_output or self.world == 1:
             return y
@@ -100,7 +109,7 @@ class ColumnParallelLinear:
 class RowParallelLinear:
     """y = sum_r x[:, K_r] . W[:, K_r]^T ; partial sums are all-reduced in fp32 (or `reduce_dtype`).
 
-    With `comm` (an `ops.Comm` of the same ranks) and M <= 8 the sum over ranks happens inside the GEMV kernel
+    With `comm` (an `ops.Comm` of the same ranks) and M <= 64 the sum over ranks happens inside the kernel
     over NVLink peer memory (fp32 partials, rank order, one rounding) and no NCCL collective is issued.
     """
 
@@ -127,10 +136,9 @@ class RowParallelLinear:
         out_dtype = out_dtype or x.dtype
         if not self.input_is_parallel:
             x = x[:, self.rank * self.K_local:(self.rank + 1) * self.K_local].contiguous()
-        if (self.comm is not None and self.compute is None and x.shape[0] <= 8 and
-                self.weight_layout == ops.QF_LAYOUT_CANONICAL):
+        if self.comm is not None and self.compute is None and x.shape[0] <= 64:
             return ops.w4a16_linear_allreduce(x, self.qweight, self.scales, self.zeros, self.comm, self.group_size,
-                                              self.zero_const, out_dtype)
+                                              self.zero_const, out_dtype, weight_layout=self.weight_layout)
         if self.compute is not None:
             y = self.compute(x, self.qweight, self.scales, self.zeros, self.group_size, self.zero_const,
                              self.reduce_dtype)

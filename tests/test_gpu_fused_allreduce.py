@@ -1,4 +1,4 @@
-"""The GEMV kernel with the cross-GPU sum in its epilogue (qf_w4a16_linear_allreduce).
+"""The linear kernels with the cross-GPU step in their epilogue (qf_w4a16_linear_allreduce / _allgather).
 
 One GPU: a comm of world 1 runs the whole exchange (push, flag, wait, sum) against its own buffer, so the result
 must equal the plain linear bit for bit, call after call (the slots alternate by call parity) and inside a CUDA
@@ -37,7 +37,8 @@ def test_world1_equals_plain_linear(M, K, N, act, split_k):
     try:
         want = qf.w4a16_linear(x, qw, sc, zr, 128, out_dtype=torch.float32, path=qf.QF_PATH_GEMV, split_k=split_k)
         for _ in range(3):  # both slot parities
-            got = qf.w4a16_linear_allreduce(x, qw, sc, zr, comm, 128, out_dtype=torch.float32, split_k=split_k)
+            got = qf.w4a16_linear_allreduce(x, qw, sc, zr, comm, 128, out_dtype=torch.float32, split_k=split_k,
+                                            path=qf.QF_PATH_GEMV)
             assert torch.equal(got, want)
         ref = O.w4a16_linear(d["x"], d["qweight"], d["scales"], d["zeros"], 128, act, O.F32, accumulate="f64")
         assert O.rel_err(got.cpu().numpy(), ref) < 1e-2
@@ -61,13 +62,13 @@ def test_world1_in_cuda_graph():
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
-            qf.w4a16_linear_allreduce(x, qw, sc, zr, comm, 128, out=out)
+            qf.w4a16_linear_allreduce(x, qw, sc, zr, comm, 128, out=out, path=qf.QF_PATH_GEMV)
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             for _ in range(3):
-                qf.w4a16_linear_allreduce(x, qw, sc, zr, comm, 128, out=out)
+                qf.w4a16_linear_allreduce(x, qw, sc, zr, comm, 128, out=out, path=qf.QF_PATH_GEMV)
         for _ in range(3):
             out.zero_()
             g.replay()
@@ -78,16 +79,45 @@ def test_world1_in_cuda_graph():
         comm.close()
 
 
+@pytest.mark.parametrize("M,K,N,act,split_k,inter", [
+    (16, 1024, 512, "bf16", 0, True), (64, 2048, 256, "f16", 1, False), (5, 4096, 1024, "bf16", 0, True),
+    (33, 1024, 384, "bf16", 2, True),
+])
+@pytest.mark.parametrize("gather", [False, True])
+def test_world1_tcgen05_kernel(M, K, N, act, split_k, inter, gather):
+    import quantforge_b200 as qf
+    from oracle import qf_oracle as O
+    dev = torch.device("cuda:0")
+    tdt = torch.float16 if act == "f16" else torch.bfloat16
+    d = O.make_inputs(M=M, K=K, N=N, group_size=128, act_dtype=act, seed=M + N)
+    x, qw, sc = _t(d["x"], dev, tdt), _t(d["qweight"], dev), _t(d["scales"], dev, tdt)
+    zr = qf.pack_zeros_u4(_t(d["zeros"], dev))
+    layout = qf.QF_LAYOUT_INTERLEAVED if inter else qf.QF_LAYOUT_CANONICAL
+    if inter:
+        qw = qf.prepack_w4(qw)
+    comm = qf.Comm(M * N, device=dev, rank=0, world=1)
+    fn = qf.w4a16_linear_allgather if gather else qf.w4a16_linear_allreduce
+    try:
+        want = qf.w4a16_linear(x, qw, sc, zr, 128, path=qf.QF_PATH_GEMM, split_k=split_k, weight_layout=layout)
+        for _ in range(3):
+            got = fn(x, qw, sc, zr, comm, 128, path=qf.QF_PATH_GEMM, split_k=split_k, weight_layout=layout)
+            assert torch.equal(got, want)
+        torch.cuda.synchronize()
+        assert qf.device_status(dev) == 0
+    finally:
+        comm.close()
+
+
 def test_rejects_what_the_kernel_cannot_do():
     import quantforge_b200 as qf
     from oracle import qf_oracle as O
     dev = torch.device("cuda:0")
-    d = O.make_inputs(M=16, K=512, N=128, group_size=128, act_dtype="bf16", seed=1)
+    d = O.make_inputs(M=80, K=512, N=128, group_size=128, act_dtype="bf16", seed=1)
     x, qw, sc = _t(d["x"], dev, torch.bfloat16), _t(d["qweight"], dev), _t(d["scales"], dev, torch.bfloat16)
     zr = qf.pack_zeros_u4(_t(d["zeros"], dev))
     comm = qf.Comm(64, device=dev, rank=0, world=1)
     try:
-        with pytest.raises(qf.QuantForgeError):   # M > 8
+        with pytest.raises(qf.QuantForgeError):   # M > 64
             qf.w4a16_linear_allreduce(x, qw, sc, zr, comm, 128)
         with pytest.raises(qf.QuantForgeError):   # M*N beyond the comm's capacity
             qf.w4a16_linear_allreduce(x[:1], qw, sc, zr, comm, 128)
@@ -117,13 +147,23 @@ def _worker(rank, world, port, out):
         import quantforge_b200 as qf
         from oracle import qf_oracle as O
         from quantforge_b200 import tp
-        comm = qf.Comm(8 * 4096, device=dev)
+        comm = qf.Comm(16 * 4096, device=dev)
         res = []
-        for (M, K, N, act) in [(1, 2048, 4096, "bf16"), (2, 1024, 528, "f16"), (8, 4096, 1024, "bf16")]:
+        for (M, K, N, act, mode) in [(1, 2048, 4096, "bf16", "row"), (2, 1024, 528, "f16", "row"),
+                                     (8, 4096, 1024, "bf16", "row"), (16, 2048, 512, "bf16", "row"),
+                                     (64, 1024, 256, "f16", "row"), (1, 1024, 2048, "bf16", "col"),
+                                     (16, 2048, 1024, "bf16", "col"), (4, 512, 96, "f16", "col")]:
             tdt = torch.float16 if act == "f16" else torch.bfloat16
             d = O.make_inputs(M=M, K=K, N=N, group_size=128, act_dtype=act, seed=K + M)
-            lin = tp.RowParallelLinear(_t(d["qweight"], dev), _t(d["scales"], dev, tdt),
-                                       qf.pack_zeros_u4(_t(d["zeros"], dev)), 128, input_is_parallel=False, comm=comm)
+            prepack = M > 2 and N % 256 == 0
+            if mode == "row":
+                lin = tp.RowParallelLinear(_t(d["qweight"], dev), _t(d["scales"], dev, tdt),
+                                           qf.pack_zeros_u4(_t(d["zeros"], dev)), 128, input_is_parallel=False,
+                                           comm=comm, prepack=prepack)
+            else:
+                lin = tp.ColumnParallelLinear(_t(d["qweight"], dev), _t(d["scales"], dev, tdt),
+                                              qf.pack_zeros_u4(_t(d["zeros"], dev)), 128, gather_output=True,
+                                              comm=comm, prepack=prepack)
             x = _t(d["x"], dev, tdt)
             want = O.w4a16_linear(d["x"], d["qweight"], d["scales"], d["zeros"], 128, act, O.F32, accumulate="f64")
             for _ in range(3):
