@@ -111,6 +111,11 @@ struct ArParams {
     int gather;                   // 0: Y[M, N] = sum over ranks; 1: Y[M, world*N], columns [r*N, (r+1)*N) from rank r
 };
 
+// Kernel argument of the exchange: an ArParams in the exchanging instantiations, an empty struct in the plain ones.
+struct NoExchange {};
+template <bool EXCH> struct ExchArg { typedef NoExchange type; };
+template <> struct ExchArg<true> { typedef ArParams type; };
+
 // Validates `d` and fills the launch plan. Returns QF_OK or an error status; `why` receives a message.
 int make_plan(const qf_linear_desc *d, Plan *p, std::string *why);
 

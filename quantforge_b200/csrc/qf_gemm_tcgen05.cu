@@ -67,7 +67,6 @@ struct GemmParams {
     int split_k;
     int interleaved;       // weight nibble order inside a word: 0 canonical, 1 pair-interleaved
     int tiled;             // 1: weights stored tile-major (QF_LAYOUT_TILED)
-    ArParams ar;           // ar.world > 0: finished tiles are exchanged across GPUs (sum or gather) before Y is written
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -236,15 +235,16 @@ __device__ __forceinline__ void convert32(const uint4 &v, const ZeroScale<BF16> 
 // ---------------------------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------------------------
-template <bool BF16, int BN, bool INTER>
+// EXCH: finished tiles are exchanged across GPUs (sum or gather) before Y is written; `ar` then is an ArParams.
+// The plain instantiations take an empty struct instead, so their parameter block and code stay what they were.
+template <bool BF16, int BN, bool INTER, bool EXCH>
 __global__ void __launch_bounds__(GEMM_THREADS, GemmCfg<BN>::CTAS_PER_SM)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-            const GemmParams p) {
+            const GemmParams p, const typename ExchArg<EXCH>::type ar) {
     using C = GemmCfg<BN>;
     constexpr int BK = C::BK;
     constexpr int STAGES = C::STAGES;
     constexpr int NA = C::NA;
-    constexpr bool EXCH = BN <= 64;  // the cross-GPU exchange serves decode batches only
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t s_tmem_base;
@@ -458,7 +458,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
         if (ok) {
             // the activations this tile consumed were requested after the dependency wait, so the previous call on
             // this rank has finished and advanced the epoch
-            const unsigned ar_epoch = (EXCH && p.ar.world > 0 && p.split_k == 1) ? exch_read_epoch(p.ar) : 0u;
+            unsigned ar_epoch = 0u;
+            if constexpr (EXCH) ar_epoch = exch_read_epoch(ar);
             constexpr int COLS_PER_WG = BN / 2;
             const int64_t Mp = (int64_t)gridDim.x * BN;
 #pragma unroll 1
@@ -473,7 +474,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                     const float v = __uint_as_float(r[j]);
                     if (p.split_k == 1) {
                         if (m < p.M) {
-                            if (EXCH && p.ar.world > 0) exch_push(p.ar, ar_epoch, (size_t)(m * p.N + n), v);
+                            if constexpr (EXCH) exch_push(ar, ar_epoch, (size_t)(m * p.N + n), v);
                             else store_out(p.Y, p.out_dtype, m * p.N + n, v);
                         }
                     } else {
@@ -499,7 +500,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
         __syncthreads();
     } else {
         bool final_cta = true;  // this CTA holds (or has pushed) the finished tile
-        const unsigned ar_epoch = (EXCH && p.ar.world > 0) ? exch_read_epoch(p.ar) : 0u;
+        unsigned ar_epoch = 0u;
+        if constexpr (EXCH) ar_epoch = exch_read_epoch(ar);
         if (p.split_k > 1) {
             // split-K: last CTA of this (m_tile, n_tile) sums the partial tiles in split order
             __threadfence();
@@ -540,9 +542,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                             }
                         }
                         const int64_t o = m * p.N + n0 + nl;
-                        if (EXCH && p.ar.world > 0) {
-                            exch_push2(p.ar, ar_epoch, (size_t)o, acc.x, acc.y);
-                            exch_push2(p.ar, ar_epoch, (size_t)o + 2, acc.z, acc.w);
+                        if constexpr (EXCH) {
+                            exch_push2(ar, ar_epoch, (size_t)o, acc.x, acc.y);
+                            exch_push2(ar, ar_epoch, (size_t)o + 2, acc.z, acc.w);
                         } else {
                             store_out(p.Y, p.out_dtype, o, acc.x);
                             store_out(p.Y, p.out_dtype, o + 1, acc.y);
@@ -553,15 +555,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                 }
             }
         }
-        if (EXCH && p.ar.world > 0 && final_cta) {
+        if constexpr (EXCH) if (final_cta) {
             // Cross-GPU step: every element of the tile has been pushed to all ranks (above, or in the epilogue);
             // collect the other ranks' values for the same elements and write the output. The pairs carry their
             // own arrival token, so no block-level synchronisation separates the pushes from the collects.
-            if (!exch_collect_tile(p.ar, ar_epoch, m0, BN, n0, 128, p.M, p.N, p.Y, p.out_dtype, tid, GEMM_THREADS,
+            if (!exch_collect_tile(ar, ar_epoch, m0, BN, n0, 128, p.M, p.N, p.Y, p.out_dtype, tid, GEMM_THREADS,
                                    abort_flag))
                 s_abort = 1;
             __syncthreads();
-            if (tid == 0) exch_block_done(p.ar, ar_epoch, gridDim.x * gridDim.y, s_abort != 0);
+            if (tid == 0) exch_block_done(ar, ar_epoch, gridDim.x * gridDim.y, s_abort != 0);
         }
     }
     if (warp == 9) {
@@ -640,13 +642,19 @@ static int get_tensor_map(qf_ctx *ctx, CUtensorMap *out, const void *ptr, int ki
     return QF_OK;
 }
 
+constexpr bool gemm_has_exchange(int bn) { return bn <= 64; }  // the cross-GPU exchange serves decode batches only
+
 template <bool BF16, int BN>
 static cudaError_t gemm_set_attr() {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BF16, BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         GemmCfg<BN>::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(gemm_kernel<BF16, BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                GemmCfg<BN>::SMEM_BYTES);
+    const int bytes = GemmCfg<BN>::SMEM_BYTES;
+    const cudaFuncAttribute attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BF16, BN, false, false>, attr, bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_kernel<BF16, BN, true, false>, attr, bytes);
+    if constexpr (gemm_has_exchange(BN)) {
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_kernel<BF16, BN, false, true>, attr, bytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_kernel<BF16, BN, true, true>, attr, bytes);
+    }
+    return e;
 }
 
 int gemm_init(qf_ctx *ctx) {
@@ -670,7 +678,7 @@ int gemm_init(qf_ctx *ctx) {
 
 template <bool BF16, int BN>
 static int gemm_launch_bn(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
-                          GemmParams &p, cudaStream_t s) {
+                          GemmParams &p, cudaStream_t s, const ArParams *ar) {
     using C = GemmCfg<BN>;
     CUtensorMap tw, tx;
     const bool tiled = d->weight_layout == QF_LAYOUT_TILED;
@@ -683,11 +691,23 @@ static int gemm_launch_bn(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan
     p.kblocks = (int)(d->K / C::BK);
     p.kblocks_per_split = plan.chunks_per_split;
     dim3 grid((unsigned)plan.m_tiles, (unsigned)(d->N / 128), (unsigned)plan.split_k);
-    const cudaError_t le =
-        p.interleaved ? launch_kernel(gemm_kernel<BF16, BN, true>, grid, dim3(GEMM_THREADS), C::SMEM_BYTES, s,
-                                      pdl_enabled(), tw, tx, p)
-                      : launch_kernel(gemm_kernel<BF16, BN, false>, grid, dim3(GEMM_THREADS), C::SMEM_BYTES, s,
-                                      pdl_enabled(), tw, tx, p);
+    const dim3 blk(GEMM_THREADS);
+    cudaError_t le;
+    if (ar) {
+        if constexpr (gemm_has_exchange(BN)) {
+            le = p.interleaved ? launch_kernel(gemm_kernel<BF16, BN, true, true>, grid, blk, C::SMEM_BYTES, s,
+                                               pdl_enabled(), tw, tx, p, *ar)
+                               : launch_kernel(gemm_kernel<BF16, BN, false, true>, grid, blk, C::SMEM_BYTES, s,
+                                               pdl_enabled(), tw, tx, p, *ar);
+        } else {
+            return fail(ctx, QF_ERR_UNSUPPORTED, "the in-kernel exchange serves M <= 64");
+        }
+    } else {
+        le = p.interleaved ? launch_kernel(gemm_kernel<BF16, BN, true, false>, grid, blk, C::SMEM_BYTES, s,
+                                           pdl_enabled(), tw, tx, p, NoExchange{})
+                           : launch_kernel(gemm_kernel<BF16, BN, false, false>, grid, blk, C::SMEM_BYTES, s,
+                                           pdl_enabled(), tw, tx, p, NoExchange{});
+    }
     g_launch_count.fetch_add(1);
     QF_CUDA_TRY(ctx, le);
     QF_CUDA_TRY(ctx, cudaGetLastError());
@@ -696,13 +716,13 @@ static int gemm_launch_bn(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan
 
 template <bool BF16>
 static int gemm_launch_dt(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
-                          GemmParams &p, cudaStream_t s) {
+                          GemmParams &p, cudaStream_t s, const ArParams *ar) {
     switch (plan.bn) {
-        case 16: return gemm_launch_bn<BF16, 16>(ctx, d, plan, X, qw, p, s);
-        case 32: return gemm_launch_bn<BF16, 32>(ctx, d, plan, X, qw, p, s);
-        case 64: return gemm_launch_bn<BF16, 64>(ctx, d, plan, X, qw, p, s);
-        case 128: return gemm_launch_bn<BF16, 128>(ctx, d, plan, X, qw, p, s);
-        case 256: return gemm_launch_bn<BF16, 256>(ctx, d, plan, X, qw, p, s);
+        case 16: return gemm_launch_bn<BF16, 16>(ctx, d, plan, X, qw, p, s, ar);
+        case 32: return gemm_launch_bn<BF16, 32>(ctx, d, plan, X, qw, p, s, ar);
+        case 64: return gemm_launch_bn<BF16, 64>(ctx, d, plan, X, qw, p, s, ar);
+        case 128: return gemm_launch_bn<BF16, 128>(ctx, d, plan, X, qw, p, s, ar);
+        case 256: return gemm_launch_bn<BF16, 256>(ctx, d, plan, X, qw, p, s, ar);
         default: return fail(ctx, QF_ERR_BAD_ARG, "bad batch tile");
     }
 }
@@ -713,7 +733,6 @@ static int launch_gemm_impl(qf_ctx *ctx, const qf_linear_desc *d, const Plan &pl
                             const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s,
                             const ArParams *ar) {
     GemmParams p;
-    p.ar = ar ? *ar : ArParams{};
     p.scales = (const uint16_t *)scales;
     p.zeros = zeros;
     p.Y = Y;
@@ -730,8 +749,8 @@ static int launch_gemm_impl(qf_ctx *ctx, const qf_linear_desc *d, const Plan &pl
     p.split_k = plan.split_k;
     p.interleaved = d->weight_layout != QF_LAYOUT_CANONICAL;
     p.tiled = d->weight_layout == QF_LAYOUT_TILED;
-    if (d->act_dtype == QF_BF16) return gemm_launch_dt<true>(ctx, d, plan, X, qw, p, s);
-    return gemm_launch_dt<false>(ctx, d, plan, X, qw, p, s);
+    if (d->act_dtype == QF_BF16) return gemm_launch_dt<true>(ctx, d, plan, X, qw, p, s, ar);
+    return gemm_launch_dt<false>(ctx, d, plan, X, qw, p, s, ar);
 }
 
 int launch_gemm(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,

@@ -47,7 +47,6 @@ struct GemvParams {
     int out_dtype;
     int zero_const;
     int m_pad;          // rows of X staged per batch tile: 1, 2, 4 or 8
-    ArParams ar;        // read by the AR (cross-GPU sum) instantiations only
 };
 
 // dynamic shared memory: ring | constants table [chunks][64 rows] uint2 | staged X [chunks][4][m_pad][4] uint4
@@ -112,8 +111,8 @@ __device__ __forceinline__ ZeroScale<BF16> consts_from(const uint2 e) {
 // A waiting block depends only on blocks that the peers dispatched before their own waiting blocks (blocks are
 // dispatched in index order and a block waits only after every block of its column has arrived), so waiters
 // cannot starve the work they wait for; the wait is bounded all the same.
-template <bool BF16, int ZMODE, int MPAD, bool AR = false>
-__global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams p) {
+template <bool BF16, int ZMODE, int MPAD, bool AR>
+__device__ __forceinline__ void gemv_body(const GemvParams &p, const typename ExchArg<AR>::type &ar) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __shared__ int s_is_last;
     __shared__ volatile int s_ar_fail;
@@ -169,7 +168,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams 
     griddep_launch_dependents();
     griddep_wait();
     unsigned ar_epoch = 0;
-    if constexpr (AR) ar_epoch = exch_read_epoch(p.ar);
+    if constexpr (AR) ar_epoch = exch_read_epoch(ar);
 
     // 3. activations of this K range in fragment order, zero rows beyond M
     {
@@ -310,7 +309,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams 
     }
 
     if constexpr (AR) {
-        const ArParams &ar = p.ar;
         // ar_epoch counts the calls completed on this comm (same value on every rank); it was read after the
         // dependency wait, i.e. after the previous call on this rank had finished and advanced it.
         if (tid == 0) s_ar_fail = 0;
@@ -334,13 +332,24 @@ __global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams 
     }
 }
 
+// Two entry points over one body: the plain kernel keeps its one-struct parameter block; the exchanging kernel
+// adds the ArParams.
+template <bool BF16, int ZMODE, int MPAD>
+__global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvParams p) {
+    gemv_body<BF16, ZMODE, MPAD, false>(p, NoExchange{});
+}
+template <bool BF16, int ZMODE, int MPAD>
+__global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_exch_kernel(const GemvParams p, const ArParams ar) {
+    gemv_body<BF16, ZMODE, MPAD, true>(p, ar);
+}
+
 template <bool BF16, int ZMODE, int MPAD>
 static cudaError_t set_attr1() {
     const int bytes = (int)gemv_smem_bytes(GEMV_MAX_CHUNKS_PER_SPLIT, MPAD);
-    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<BF16, ZMODE, MPAD, false>,
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<BF16, ZMODE, MPAD>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(gemv_kernel<BF16, ZMODE, MPAD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(gemv_exch_kernel<BF16, ZMODE, MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  bytes);
     return e;
 }
@@ -363,32 +372,37 @@ int gemv_init(qf_ctx *ctx) {
     return QF_OK;
 }
 
-template <bool BF16, int ZMODE, bool AR>
-static cudaError_t gemv_dispatch_m(dim3 grid, size_t smem, cudaStream_t s, const GemvParams &p) {
+template <bool BF16, int ZMODE>
+static cudaError_t gemv_dispatch_m(dim3 grid, size_t smem, cudaStream_t s, const GemvParams &p, const ArParams *ar) {
     const dim3 blk(GEMV_THREADS);
+    const bool pdl = pdl_enabled();
+    if (ar) {
+        switch (p.m_pad) {
+            case 1: return launch_kernel(gemv_exch_kernel<BF16, ZMODE, 1>, grid, blk, smem, s, pdl, p, *ar);
+            case 2: return launch_kernel(gemv_exch_kernel<BF16, ZMODE, 2>, grid, blk, smem, s, pdl, p, *ar);
+            case 4: return launch_kernel(gemv_exch_kernel<BF16, ZMODE, 4>, grid, blk, smem, s, pdl, p, *ar);
+            default: return launch_kernel(gemv_exch_kernel<BF16, ZMODE, 8>, grid, blk, smem, s, pdl, p, *ar);
+        }
+    }
     switch (p.m_pad) {
-        case 1: return launch_kernel(gemv_kernel<BF16, ZMODE, 1, AR>, grid, blk, smem, s, pdl_enabled(), p);
-        case 2: return launch_kernel(gemv_kernel<BF16, ZMODE, 2, AR>, grid, blk, smem, s, pdl_enabled(), p);
-        case 4: return launch_kernel(gemv_kernel<BF16, ZMODE, 4, AR>, grid, blk, smem, s, pdl_enabled(), p);
-        default: return launch_kernel(gemv_kernel<BF16, ZMODE, 8, AR>, grid, blk, smem, s, pdl_enabled(), p);
+        case 1: return launch_kernel(gemv_kernel<BF16, ZMODE, 1>, grid, blk, smem, s, pdl, p);
+        case 2: return launch_kernel(gemv_kernel<BF16, ZMODE, 2>, grid, blk, smem, s, pdl, p);
+        case 4: return launch_kernel(gemv_kernel<BF16, ZMODE, 4>, grid, blk, smem, s, pdl, p);
+        default: return launch_kernel(gemv_kernel<BF16, ZMODE, 8>, grid, blk, smem, s, pdl, p);
     }
 }
-template <bool BF16, bool AR>
-static cudaError_t gemv_dispatch_z(int zmode, dim3 grid, size_t smem, cudaStream_t s, const GemvParams &p) {
-    if (zmode == QF_ZERO_CONST) return gemv_dispatch_m<BF16, QF_ZERO_CONST, AR>(grid, smem, s, p);
-    if (zmode == QF_ZERO_U4) return gemv_dispatch_m<BF16, QF_ZERO_U4, AR>(grid, smem, s, p);
-    return gemv_dispatch_m<BF16, QF_ZERO_I8, AR>(grid, smem, s, p);
-}
 template <bool BF16>
-static cudaError_t gemv_dispatch(int zmode, dim3 grid, size_t smem, cudaStream_t s, const GemvParams &p, bool ar) {
-    return ar ? gemv_dispatch_z<BF16, true>(zmode, grid, smem, s, p) : gemv_dispatch_z<BF16, false>(zmode, grid, smem, s, p);
+static cudaError_t gemv_dispatch(int zmode, dim3 grid, size_t smem, cudaStream_t s, const GemvParams &p,
+                                 const ArParams *ar) {
+    if (zmode == QF_ZERO_CONST) return gemv_dispatch_m<BF16, QF_ZERO_CONST>(grid, smem, s, p, ar);
+    if (zmode == QF_ZERO_U4) return gemv_dispatch_m<BF16, QF_ZERO_U4>(grid, smem, s, p, ar);
+    return gemv_dispatch_m<BF16, QF_ZERO_I8>(grid, smem, s, p, ar);
 }
 
 static int launch_gemv_impl(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
                             const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s,
                             const ArParams *ar) {
     GemvParams p;
-    p.ar = ar ? *ar : ArParams{};
     p.X = (const uint16_t *)X;
     p.qw = (const uint32_t *)qw;
     p.scales = (const uint16_t *)scales;
@@ -410,8 +424,8 @@ static int launch_gemv_impl(qf_ctx *ctx, const qf_linear_desc *d, const Plan &pl
     const int64_t m_in_tile = d->M < 8 ? d->M : 8;
     p.m_pad = m_in_tile <= 1 ? 1 : m_in_tile <= 2 ? 2 : m_in_tile <= 4 ? 4 : 8;
     const size_t smem = gemv_smem_bytes(plan.chunks_per_split, p.m_pad);
-    const cudaError_t le = d->act_dtype == QF_BF16 ? gemv_dispatch<true>(d->zero_mode, grid, smem, s, p, ar != nullptr)
-                                                   : gemv_dispatch<false>(d->zero_mode, grid, smem, s, p, ar != nullptr);
+    const cudaError_t le = d->act_dtype == QF_BF16 ? gemv_dispatch<true>(d->zero_mode, grid, smem, s, p, ar)
+                                                   : gemv_dispatch<false>(d->zero_mode, grid, smem, s, p, ar);
     g_launch_count.fetch_add(1);
     QF_CUDA_TRY(ctx, le);
     QF_CUDA_TRY(ctx, cudaGetLastError());
