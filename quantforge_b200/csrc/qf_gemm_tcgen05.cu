@@ -21,6 +21,7 @@
 // No multicast, no cluster launch: every CTA loads its own tiles.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -67,6 +68,8 @@ struct GemmParams {
     int split_k;
     int interleaved;       // weight nibble order inside a word: 0 canonical, 1 pair-interleaved
     int tiled;             // 1: weights stored tile-major (QF_LAYOUT_TILED)
+    int cluster_reduce;    // 1: the split_k blocks of a tile form a thread-block cluster and sum their partial
+                           //    tiles through distributed shared memory (no global partials, no counters)
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -121,6 +124,25 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
+}
+// Thread-block cluster: barrier over all threads of all blocks of the cluster, and loads from a peer block's
+// shared memory (distributed shared memory).
+__device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t cta_rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(cta_rank));
+    return r;
+}
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(addr)
+                 : "memory");
+    return v;
 }
 // Untiled bulk copy global -> shared (16-byte aligned, size a multiple of 16), completion on an mbarrier.
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
@@ -245,6 +267,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
     constexpr int BK = C::BK;
     constexpr int STAGES = C::STAGES;
     constexpr int NA = C::NA;
+    constexpr bool CLUSTER_OK = BN <= 64 && !EXCH;  // the cluster reduction serves the narrow split-K tiles
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t s_tmem_base;
@@ -477,6 +500,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                             if constexpr (EXCH) exch_push(ar, ar_epoch, (size_t)(m * p.N + n), v);
                             else store_out(p.Y, p.out_dtype, m * p.N + n, v);
                         }
+                    } else if (CLUSTER_OK && p.cluster_reduce) {
+                        // partial tile [batch row][weight row] fp32 in the (now idle) pipeline stages
+                        asm volatile("st.shared.f32 [%0], %1;" ::"r"(smem_base + (uint32_t)((col + j) * 128 + row) * 4u),
+                                     "f"(v)
+                                     : "memory");
                     } else {
                         __stcg(p.partial + ((int64_t)split * Mp + m) * p.N + n, v);
                     }
@@ -488,7 +516,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
     // ------------------------------ teardown ------------------------------
     tc_fence_before();
     __syncthreads();
-    if (s_abort) {
+    if (CLUSTER_OK && p.cluster_reduce) {
+        // Split-K inside a cluster: the split_k blocks of this tile are the blocks of one cluster (rank = split).
+        // Every block, aborted or not, passes both cluster barriers, so no block can wait for one that left.
+        if (s_abort && warp == 8 && producer_issued > 0) {
+            int dummy = 0;
+            volatile int *no_abort = &dummy;
+            for (int it = max(0, producer_issued - STAGES); it < producer_issued; ++it)
+                mbar_wait(full_bar(it % STAGES), (it / STAGES) & 1, no_abort);
+        }
+        if (s_abort && tid == 0) atomicExch(p.status, QF_ERR_TIMEOUT);
+        cluster_sync_all();  // all partial tiles are in shared memory
+        if (!s_abort) {
+            // each block sums its share of the tile from all blocks in split order and writes the output
+            const int units = 32 * BN;  // float4 units of the tile
+            const int per = (units + p.split_k - 1) / p.split_k;
+            const int u_end = min(units, (split + 1) * per);
+            for (int u = split * per + tid; u < u_end; u += GEMM_THREADS) {
+                const int nl = (u & 31) * 4;
+                const int64_t m = m0 + (u >> 5);
+                if (m < p.M) {
+                    const uint32_t a = smem_base + (uint32_t)((u >> 5) * 128 + nl) * 4u;
+                    float4 v[8];
+#pragma unroll
+                    for (int sp = 0; sp < 8; ++sp)
+                        v[sp] = sp < p.split_k ? ld_dsmem_f4(dsmem_addr(a, (uint32_t)sp)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int sp = 0; sp < 8; ++sp) {
+                        acc.x += v[sp].x;
+                        acc.y += v[sp].y;
+                        acc.z += v[sp].z;
+                        acc.w += v[sp].w;
+                    }
+                    const int64_t o = m * p.N + n0 + nl;
+                    store_out(p.Y, p.out_dtype, o, acc.x);
+                    store_out(p.Y, p.out_dtype, o + 1, acc.y);
+                    store_out(p.Y, p.out_dtype, o + 2, acc.z);
+                    store_out(p.Y, p.out_dtype, o + 3, acc.w);
+                }
+            }
+        }
+        cluster_sync_all();  // nobody leaves while its tile may still be read
+    } else if (s_abort) {
         if (warp == 8 && producer_issued > 0) {
             // drain this CTA's own TMA copies before the shared memory goes away
             int dummy = 0;
@@ -642,6 +712,15 @@ static int get_tensor_map(qf_ctx *ctx, CUtensorMap *out, const void *ptr, int ki
     return QF_OK;
 }
 
+// QF_CLUSTER_REDUCE=0 in the environment keeps split-K on the global-memory path (partial tiles + counters).
+static bool cluster_reduce_enabled() {
+    static const bool on = [] {
+        const char *e = std::getenv("QF_CLUSTER_REDUCE");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 constexpr bool gemm_has_exchange(int bn) { return bn <= 64; }  // the cross-GPU exchange serves decode batches only
 
 template <bool BF16, int BN>
@@ -703,10 +782,16 @@ static int gemm_launch_bn(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan
             return fail(ctx, QF_ERR_UNSUPPORTED, "the in-kernel exchange serves M <= 64");
         }
     } else {
-        le = p.interleaved ? launch_kernel(gemm_kernel<BF16, BN, true, false>, grid, blk, C::SMEM_BYTES, s,
-                                           pdl_enabled(), tw, tx, p, NoExchange{})
-                           : launch_kernel(gemm_kernel<BF16, BN, false, false>, grid, blk, C::SMEM_BYTES, s,
-                                           pdl_enabled(), tw, tx, p, NoExchange{});
+        // 2..8 splits of a narrow tile: one thread-block cluster per tile sums the partial tiles on chip
+        unsigned cluster_z = 1;
+        if (BN <= 64 && plan.split_k >= 2 && plan.split_k <= 8 && cluster_reduce_enabled()) {
+            p.cluster_reduce = 1;
+            cluster_z = (unsigned)plan.split_k;
+        }
+        le = p.interleaved ? launch_kernel_z(gemm_kernel<BF16, BN, true, false>, grid, blk, C::SMEM_BYTES, s,
+                                             pdl_enabled(), cluster_z, tw, tx, p, NoExchange{})
+                           : launch_kernel_z(gemm_kernel<BF16, BN, false, false>, grid, blk, C::SMEM_BYTES, s,
+                                             pdl_enabled(), cluster_z, tw, tx, p, NoExchange{});
     }
     g_launch_count.fetch_add(1);
     QF_CUDA_TRY(ctx, le);
@@ -749,6 +834,7 @@ static int launch_gemm_impl(qf_ctx *ctx, const qf_linear_desc *d, const Plan &pl
     p.split_k = plan.split_k;
     p.interleaved = d->weight_layout != QF_LAYOUT_CANONICAL;
     p.tiled = d->weight_layout == QF_LAYOUT_TILED;
+    p.cluster_reduce = 0;
     if (d->act_dtype == QF_BF16) return gemm_launch_dt<true>(ctx, d, plan, X, qw, p, s, ar);
     return gemm_launch_dt<false>(ctx, d, plan, X, qw, p, s, ar);
 }
