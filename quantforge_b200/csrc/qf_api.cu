@@ -17,6 +17,14 @@ bool pdl_enabled() {
     return on;
 }
 
+bool cluster_reduce_enabled() {
+    static const bool on = [] {
+        const char *e = std::getenv("QF_CLUSTER_REDUCE");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 static constexpr int kSmCount = 148;  // planning constant: the library targets B200 only
 // The split-K arrival counters occupy a FIXED region at the start of the workspace, so that a
 // workspace reused by linears of different shapes never exposes stale partial sums as counters.
@@ -81,6 +89,8 @@ int make_plan(const qf_linear_desc *d, Plan *p, std::string *why) {
             if (split < 1) split = 1;
         }
         if (split > chunks) split = chunks;
+        if (d->split_k == 0 && split > 8 && split <= 10 && chunks % 8 == 0 && chunks / 8 <= 32)
+            split = 8;  // an even split that fits one thread-block cluster (on-chip reduction)
         int cps = (chunks + split - 1) / split;
         if (cps > 32) cps = 32;
         split = (chunks + cps - 1) / cps;

@@ -44,6 +44,7 @@ extern std::atomic<long long> g_launch_count;
 // The linear kernels use the head start for what does not depend on the previous kernel: weight streams,
 // converter constants, barrier and TMEM set-up. QF_PDL=0 in the environment turns it off.
 bool pdl_enabled();
+bool cluster_reduce_enabled();
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
@@ -61,10 +62,10 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
-// Same, with the grid's z dimension grouped into thread-block clusters of `cluster_z` blocks (1: no clusters).
+// Same, with the grid grouped into thread-block clusters of `cluster` blocks ((1,1,1): no clusters).
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_kernel_z(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
-                                   bool pdl, unsigned cluster_z, Args &&...args) {
+inline cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                         bool pdl, dim3 cluster, Args &&...args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -77,11 +78,11 @@ inline cudaError_t launch_kernel_z(void (*kernel)(KArgs...), dim3 grid, dim3 blo
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;
     }
-    if (cluster_z > 1) {
+    if (cluster.x * cluster.y * cluster.z > 1) {
         attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = 1;
-        attr[n].val.clusterDim.y = 1;
-        attr[n].val.clusterDim.z = cluster_z;
+        attr[n].val.clusterDim.x = cluster.x;
+        attr[n].val.clusterDim.y = cluster.y;
+        attr[n].val.clusterDim.z = cluster.z;
         ++n;
     }
     cfg.attrs = attr;
@@ -287,6 +288,34 @@ __device__ __forceinline__ void store_out(void *Y, int out_dtype, int64_t idx, f
     } else {
         reinterpret_cast<__nv_bfloat16 *>(Y)[idx] = __float2bfloat16_rn(v);
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Thread-block clusters: barrier over all threads of all blocks of the cluster, and loads from a peer block's
+// shared memory (distributed shared memory). QF_CLUSTER_REDUCE=0 in the environment keeps split-K on the
+// global-memory path (partial tiles + arrival counters).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t cta_rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(cta_rank));
+    return r;
+}
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(addr)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ float ld_dsmem_f1(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
 }
 
 // ---------------------------------------------------------------------------------------------

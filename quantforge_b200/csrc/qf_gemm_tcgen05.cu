@@ -125,25 +125,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
 }
-// Thread-block cluster: barrier over all threads of all blocks of the cluster, and loads from a peer block's
-// shared memory (distributed shared memory).
-__device__ __forceinline__ void cluster_sync_all() {
-    __syncwarp();
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t cta_rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(cta_rank));
-    return r;
-}
-__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t addr) {
-    float4 v;
-    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                 : "r"(addr)
-                 : "memory");
-    return v;
-}
 // Untiled bulk copy global -> shared (16-byte aligned, size a multiple of 16), completion on an mbarrier.
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -712,15 +693,6 @@ static int get_tensor_map(qf_ctx *ctx, CUtensorMap *out, const void *ptr, int ki
     return QF_OK;
 }
 
-// QF_CLUSTER_REDUCE=0 in the environment keeps split-K on the global-memory path (partial tiles + counters).
-static bool cluster_reduce_enabled() {
-    static const bool on = [] {
-        const char *e = std::getenv("QF_CLUSTER_REDUCE");
-        return !(e && e[0] == '0');
-    }();
-    return on;
-}
-
 constexpr bool gemm_has_exchange(int bn) { return bn <= 64; }  // the cross-GPU exchange serves decode batches only
 
 template <bool BF16, int BN>
@@ -788,10 +760,10 @@ static int gemm_launch_bn(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan
             p.cluster_reduce = 1;
             cluster_z = (unsigned)plan.split_k;
         }
-        le = p.interleaved ? launch_kernel_z(gemm_kernel<BF16, BN, true, false>, grid, blk, C::SMEM_BYTES, s,
-                                             pdl_enabled(), cluster_z, tw, tx, p, NoExchange{})
-                           : launch_kernel_z(gemm_kernel<BF16, BN, false, false>, grid, blk, C::SMEM_BYTES, s,
-                                             pdl_enabled(), cluster_z, tw, tx, p, NoExchange{});
+        le = p.interleaved ? launch_kernel_cluster(gemm_kernel<BF16, BN, true, false>, grid, blk, C::SMEM_BYTES, s,
+                                             pdl_enabled(), dim3(1, 1, cluster_z), tw, tx, p, NoExchange{})
+                           : launch_kernel_cluster(gemm_kernel<BF16, BN, false, false>, grid, blk, C::SMEM_BYTES, s,
+                                             pdl_enabled(), dim3(1, 1, cluster_z), tw, tx, p, NoExchange{});
     }
     g_launch_count.fetch_add(1);
     QF_CUDA_TRY(ctx, le);
