@@ -310,7 +310,7 @@ def main():
         for M in SWEEP_MS:
             qw = torch.randint(-128, 128, (Nl, K // 2), dtype=torch.int8, device=dev, generator=gen)
             # one-time, untimed weight prepack for the linears the tcgen05 kernel serves (M > 2)
-            layout = LAYOUT_INTERLEAVED if (M > 2 and Nl % 128 == 0) else LAYOUT_CANONICAL
+            layout = LAYOUT_INTERLEAVED if ((M > 2 or Nl * K // 2 >= (32 << 20)) and Nl % 128 == 0) else LAYOUT_CANONICAL
             if layout != LAYOUT_CANONICAL:
                 qw = qf.prepack_w4(qw, layout=layout)
             sc = (torch.randn(G, Nl, device=dev, generator=gen).abs() * (0.02 / 7.0)).clamp_min(2.0 ** -14).to(
@@ -457,7 +457,7 @@ def main():
         wbytes = K * N // 2
         n = copies or max(3, -(-300_000_000 // wbytes))
         G = K // GROUP
-        layout = LAYOUT_INTERLEAVED if (M > 2 and N % 128 == 0) else LAYOUT_CANONICAL
+        layout = LAYOUT_INTERLEAVED if ((M > 2 or N * K // 2 >= (32 << 20)) and N % 128 == 0) else LAYOUT_CANONICAL
         sets = []
         for _ in range(n):
             qw = torch.randint(-128, 128, (N, K // 2), dtype=torch.int8, device=dev, generator=gen)

@@ -60,7 +60,14 @@ int make_plan(const qf_linear_desc *d, Plan *p, std::string *why) {
         if (d->reserved[i] != 0) return bad(QF_ERR_BAD_ARG, "reserved fields must be zero");
 
     int path = d->path;
-    if (path == QF_PATH_AUTO) path = (d->M <= 2) ? QF_PATH_GEMV : QF_PATH_GEMM;
+    if (path == QF_PATH_AUTO) {
+        // M <= 2: the GEMV kernel wins on small matrices (short start-up, 4 blocks per SM); from about 32 MB of
+        // weights the tcgen05 kernel streams faster (measured M=1: 59 MB 32.8 vs 22.2 us, 117 MB 56.5 vs 36.8 us)
+        // if the weights are in the layout it converts fastest.
+        const bool big = d->K * d->N / 2 >= ((int64_t)32 << 20) && d->N % 128 == 0 &&
+                         d->weight_layout != QF_LAYOUT_CANONICAL;
+        path = (d->M <= 2 && !big) ? QF_PATH_GEMV : QF_PATH_GEMM;
+    }
     if (path != QF_PATH_GEMV && path != QF_PATH_GEMM) return bad(QF_ERR_BAD_ARG, "unknown path");
     if (path == QF_PATH_GEMM && d->N % 128 != 0) {
         if (d->path == QF_PATH_GEMM) return bad(QF_ERR_BAD_ARG, "the GEMM path needs N to be a multiple of 128");

@@ -755,10 +755,15 @@ static int gemm_launch_bn(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan
         }
     } else {
         // 2..8 splits of a narrow tile: one thread-block cluster per tile sums the partial tiles on chip
+        // Clusters are placed inside one GPC, which leaves block slots unused where the GPC's slot count is not a
+        // multiple of the cluster size; a launch that no longer fits in one wave loses more than the on-chip
+        // reduction gains (measured: 32 x 8, 80 x 3, 112 x 2 blocks fit; 48 x 6 = 288 of the 296 slots do not).
         unsigned cluster_z = 1;
         if (BN <= 64 && plan.split_k >= 2 && plan.split_k <= 8 && cluster_reduce_enabled()) {
-            p.cluster_reduce = 1;
-            cluster_z = (unsigned)plan.split_k;
+            if ((int64_t)grid.x * grid.y * grid.z <= 256) {
+                p.cluster_reduce = 1;
+                cluster_z = (unsigned)plan.split_k;
+            }
         }
         le = p.interleaved ? launch_kernel_cluster(gemm_kernel<BF16, BN, true, false>, grid, blk, C::SMEM_BYTES, s,
                                              pdl_enabled(), dim3(1, 1, cluster_z), tw, tx, p, NoExchange{})

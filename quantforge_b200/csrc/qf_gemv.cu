@@ -406,6 +406,13 @@ int gemv_init(qf_ctx *ctx) {
     return QF_OK;
 }
 
+// Plain launch; p.cluster_reduce groups the split_k blocks of a column block into a thread-block cluster.
+static cudaError_t gemv_launch_plain(void (*kernel)(GemvParams), dim3 grid, dim3 blk, size_t smem, cudaStream_t s,
+                                     bool pdl, const GemvParams &p) {
+    const dim3 cl(1, p.cluster_reduce ? (unsigned)p.split_k : 1u, 1);
+    return launch_kernel_cluster(kernel, grid, blk, smem, s, pdl, cl, p);
+}
+
 template <bool BF16, int ZMODE>
 static cudaError_t gemv_dispatch_m(dim3 grid, size_t smem, cudaStream_t s, const GemvParams &p, const ArParams *ar) {
     const dim3 blk(GEMV_THREADS);
@@ -418,12 +425,11 @@ static cudaError_t gemv_dispatch_m(dim3 grid, size_t smem, cudaStream_t s, const
             default: return launch_kernel(gemv_exch_kernel<BF16, ZMODE, 8>, grid, blk, smem, s, pdl, p, *ar);
         }
     }
-    const dim3 cl(1, p.cluster_reduce ? (unsigned)p.split_k : 1u, 1);
     switch (p.m_pad) {
-        case 1: return launch_kernel_cluster(gemv_kernel<BF16, ZMODE, 1>, grid, blk, smem, s, pdl, cl, p);
-        case 2: return launch_kernel_cluster(gemv_kernel<BF16, ZMODE, 2>, grid, blk, smem, s, pdl, cl, p);
-        case 4: return launch_kernel_cluster(gemv_kernel<BF16, ZMODE, 4>, grid, blk, smem, s, pdl, cl, p);
-        default: return launch_kernel_cluster(gemv_kernel<BF16, ZMODE, 8>, grid, blk, smem, s, pdl, cl, p);
+        case 1: return gemv_launch_plain(gemv_kernel<BF16, ZMODE, 1>, grid, blk, smem, s, pdl, p);
+        case 2: return gemv_launch_plain(gemv_kernel<BF16, ZMODE, 2>, grid, blk, smem, s, pdl, p);
+        case 4: return gemv_launch_plain(gemv_kernel<BF16, ZMODE, 4>, grid, blk, smem, s, pdl, p);
+        default: return gemv_launch_plain(gemv_kernel<BF16, ZMODE, 8>, grid, blk, smem, s, pdl, p);
     }
 }
 template <bool BF16>
@@ -457,8 +463,10 @@ static int launch_gemv_impl(qf_ctx *ctx, const qf_linear_desc *d, const Plan &pl
     // 2..8 short splits: one thread-block cluster per column block sums the partial outputs on chip. The blocks of a
     // cluster leave together, so with long splits the slots they hold cost more than the global-memory tail saves
     // (measured: M=1 4096x4096, 4 chunks per split, 6.9 -> 6.5 us; 4096x14336 and 14336x4096, 11-14 chunks, 3-4 % slower).
+    // Clusters are placed inside one GPC, so a launch close to the 592 block slots would spill into a second wave.
+    const int64_t blocks = (int64_t)((d->N + GEMV_ROWS_PER_BLOCK - 1) / GEMV_ROWS_PER_BLOCK) * plan.split_k * plan.m_tiles;
     p.cluster_reduce = (!ar && plan.split_k >= 2 && plan.split_k <= 8 && plan.chunks_per_split <= 8 &&
-                        cluster_reduce_enabled())
+                        blocks <= 512 && cluster_reduce_enabled())
                            ? 1
                            : 0;
     dim3 grid((unsigned)((d->N + GEMV_ROWS_PER_BLOCK - 1) / GEMV_ROWS_PER_BLOCK), (unsigned)plan.split_k,

@@ -21,10 +21,13 @@ LLAMA3_70B = {"hidden": 8192, "kv": 1024, "ffn": 28672, "layers": 80}
 GROUP = 128
 
 
+BIG_WEIGHT_BYTES = 32 << 20  # from here on the tcgen05 kernel serves M <= 2 as well (prepacked weights)
+
+
 def _rand_linear(N, K, dtype, dev, gen, prepack):
     qw = torch.randint(-128, 128, (N, K // 2), dtype=torch.int8, device=dev, generator=gen)
     layout = QF_LAYOUT_CANONICAL
-    if prepack and N % 128 == 0:
+    if (prepack or N * K // 2 >= BIG_WEIGHT_BYTES) and N % 128 == 0:
         qw = ops.prepack_w4(qw)
         layout = QF_LAYOUT_INTERLEAVED
     G = K // GROUP
