@@ -48,8 +48,9 @@ typedef enum qf_status {
 typedef enum qf_dtype { QF_F16 = 0, QF_BF16 = 1, QF_F32 = 2 } qf_dtype;
 typedef enum qf_zero_mode { QF_ZERO_CONST = 0, QF_ZERO_U4 = 1, QF_ZERO_I8 = 2 } qf_zero_mode;
 
-/* Which kernel family serves a linear.  AUTO: M <= 2 -> GEMV kernel, M >= 3 -> tcgen05 GEMM kernel
- * (measured crossover on B200); prepacked weights and N % 128 != 0 override it, see qf_w4a16_plan. */
+/* Which kernel family serves a linear.  AUTO: M <= 2 -> GEMV kernel unless the weight matrix is large (32 MB
+ * prepacked, 40 MB canonical), M >= 3 -> tcgen05 GEMM kernel (measured crossovers on B200); prepacked weights
+ * and N % 128 != 0 override it, see qf_w4a16_plan. */
 typedef enum qf_path { QF_PATH_AUTO = 0, QF_PATH_GEMV = 1, QF_PATH_GEMM = 2 } qf_path;
 
 /*

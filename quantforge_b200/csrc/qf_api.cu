@@ -61,11 +61,12 @@ int make_plan(const qf_linear_desc *d, Plan *p, std::string *why) {
 
     int path = d->path;
     if (path == QF_PATH_AUTO) {
-        // M <= 2: the GEMV kernel wins on small matrices (short start-up, 4 blocks per SM); from about 32 MB of
-        // weights the tcgen05 kernel streams faster (measured M=1: 59 MB 32.8 vs 22.2 us, 117 MB 56.5 vs 36.8 us)
-        // if the weights are in the layout it converts fastest.
-        const bool big = d->K * d->N / 2 >= ((int64_t)32 << 20) && d->N % 128 == 0 &&
-                         d->weight_layout != QF_LAYOUT_CANONICAL;
+        // M <= 2: the GEMV kernel wins on small matrices (short start-up, 4 blocks per SM); on large ones the tcgen05
+        // kernel streams faster (measured at M=1: 42 MB 24.4 vs 17.7 us, 59 MB 33.0 vs 22.0 us, 117 MB 56.5 vs
+        // 36.5 us with prepacked weights; 19.8 / 24.7 / 41.7 us with canonical ones; a tie around 32 MB).
+        const int64_t wbytes = d->K * d->N / 2;
+        const bool big = d->N % 128 == 0 &&
+                         wbytes >= (d->weight_layout == QF_LAYOUT_CANONICAL ? (int64_t)40 << 20 : (int64_t)32 << 20);
         path = (d->M <= 2 && !big) ? QF_PATH_GEMV : QF_PATH_GEMM;
     }
     if (path != QF_PATH_GEMV && path != QF_PATH_GEMM) return bad(QF_ERR_BAD_ARG, "unknown path");
