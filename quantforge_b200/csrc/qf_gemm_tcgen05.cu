@@ -18,7 +18,9 @@
 //                    B (= X tile, K-major, 128-byte swizzle) from shared memory, fp32 accumulate in TMEM.
 // Every mbarrier wait is bounded: on expiry the CTA raises an abort flag, records QF_ERR_TIMEOUT in
 // the context's status word, drains its own TMA copies, frees its TMEM and returns.
-// No multicast, no cluster launch: every CTA loads its own tiles.
+// Every CTA loads its own tiles (plain TMA loads). Split-K over 2..8 blocks runs as a thread-block cluster whose
+// blocks sum their partial tiles through distributed shared memory; other splits use global partial tiles and an
+// arrival counter. Both cluster barriers are passed by every block, aborted or not.
 #include <cuda.h>
 
 #include <cstdlib>
