@@ -140,3 +140,49 @@ def test_gemm_rejects_bad_n(qf):
     assert e.value.status == -1
     # AUTO falls back to the GEMV kernel for such N
     assert torch.all(qf.w4a16_linear(x, qw, s) == 0)
+
+
+def _device_inputs(qf, M, K, N, sym, sigma, seed, dtype=torch.bfloat16):
+    """Inputs of a benchmark-size layer generated on the device (a CPU generator would take minutes)."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    G = K // 128
+    qw = torch.randint(-128, 128, (N, K // 2), dtype=torch.int8, device="cuda", generator=gen)
+    sc = (torch.randn(G, N, device="cuda", generator=gen).abs() * (sigma / 7.0)).clamp_min(2.0 ** -14).to(dtype)
+    zeros = None if sym else torch.randint(0, 16, (G, N), dtype=torch.int8, device="cuda", generator=gen)
+    x = torch.randn(M, K, device="cuda", generator=gen).to(dtype)
+    return qw, sc, zeros, x
+
+
+def test_prefill_full_size_sampled_columns_vs_oracle(qf):
+    """The prefill configuration at its full size (M=2048, K=8192, N=28672, symmetric, bf16): 48 output columns
+    spread over the matrix are recomputed by the CPU oracle from the same device-generated inputs."""
+    M, K, N = 2048, 8192, 28672
+    qw, sc, _, x = _device_inputs(qf, M, K, N, sym=True, sigma=0.01, seed=11)
+    y = qf.w4a16_linear(x, qf.prepack_w4(qw), sc, None, group_size=128, zero_const=8, out_dtype=torch.float32,
+                        weight_layout=INTERLEAVED)
+    assert qf.device_status() == 0
+    cols = torch.linspace(0, N - 1, 48).long().cuda()
+    want = O.w4a16_linear(x.float().cpu().numpy(), qw[cols].cpu().numpy(), sc[:, cols].float().cpu().numpy(), 8, 128,
+                          "bf16", O.F32, accumulate="f64")
+    assert O.rel_err(y[:, cols].cpu().numpy(), want) < 1e-2
+
+
+@pytest.mark.parametrize("K,N", [(28672, 8192), (8192, 10240)])
+def test_large_decode_linears_both_kernels_agree(qf, K, N):
+    """Llama-3-70B-shaped linears at M=1 and 2: AUTO sends them to the tcgen05 kernel; the GEMV kernel must give
+    the same result up to accumulation order, and 32 sampled columns must match the oracle."""
+    for M in (1, 2):
+        qw, sc, zeros, x = _device_inputs(qf, M, K, N, sym=False, sigma=0.02, seed=K + M)
+        zp = qf.pack_zeros_u4(zeros)
+        y_auto = qf.w4a16_linear(x, qf.prepack_w4(qw), sc, zp, out_dtype=torch.float32, weight_layout=INTERLEAVED)
+        y_canon = qf.w4a16_linear(x, qw, sc, zp, out_dtype=torch.float32)                    # AUTO, canonical weights
+        y_gemv = qf.w4a16_linear(x, qw, sc, zp, out_dtype=torch.float32, path=qf.QF_PATH_GEMV)
+        assert qf.device_status() == 0
+        rms = y_gemv.pow(2).mean().sqrt()
+        assert ((y_auto - y_gemv).abs().max() / rms).item() < 1e-4
+        assert ((y_canon - y_gemv).abs().max() / rms).item() < 1e-4
+        cols = torch.linspace(0, N - 1, 32).long().cuda()
+        want = O.w4a16_linear(x.float().cpu().numpy(), qw[cols].cpu().numpy(), sc[:, cols].float().cpu().numpy(),
+                              zeros[:, cols].cpu().numpy(), 128, "bf16", O.F32, accumulate="f64")
+        assert O.rel_err(y_auto[:, cols].cpu().numpy(), want) < 1e-2
