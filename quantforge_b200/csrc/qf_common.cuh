@@ -45,6 +45,10 @@ extern std::atomic<long long> g_launch_count;
 // converter constants, barrier and TMEM set-up. QF_PDL=0 in the environment turns it off.
 bool pdl_enabled();
 bool cluster_reduce_enabled();
+// Largest launch of the tcgen05 kernel (2 blocks per SM) that runs as one wave of thread-block clusters: clusters
+// are placed inside one GPC, which leaves block slots unused where the GPC's slot count is not a multiple of the
+// cluster size (measured: 32 x 8, 80 x 3, 112 x 2 blocks fit; 48 x 6 = 288 of the 296 slots do not).
+constexpr int kClusterMaxBlocks = 256;
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,

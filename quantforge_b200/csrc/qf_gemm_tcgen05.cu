@@ -762,7 +762,7 @@ static int gemm_launch_bn(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan
         // reduction gains (measured: 32 x 8, 80 x 3, 112 x 2 blocks fit; 48 x 6 = 288 of the 296 slots do not).
         unsigned cluster_z = 1;
         if (BN <= 64 && plan.split_k >= 2 && plan.split_k <= 8 && cluster_reduce_enabled()) {
-            if ((int64_t)grid.x * grid.y * grid.z <= 256) {
+            if ((int64_t)grid.x * grid.y * grid.z <= kClusterMaxBlocks) {
                 p.cluster_reduce = 1;
                 cluster_z = (unsigned)plan.split_k;
             }

@@ -51,3 +51,12 @@ def test_even_k_splits_are_preferred():
 def test_no_split_when_tiles_fill_the_device():
     assert _plan(2048, 8192, 28672, 1) == (_lib.QF_PATH_GEMM, 1)
     assert _plan(64, 8192, 28672, 1) == (_lib.QF_PATH_GEMM, 1)
+
+
+def test_splits_stay_within_one_wave_of_clusters():
+    # tcgen05 kernel, narrow tiles: at most 8 splits and at most 256 blocks, so that the split-K sum stays on chip
+    assert _plan(16, 4096, 6144, 1) == (_lib.QF_PATH_GEMM, 5)     # 48 tiles: 6 splits would be 288 blocks
+    assert _plan(64, 4096, 5120, 1) == (_lib.QF_PATH_GEMM, 6)     # 40 tiles
+    assert _plan(16, 8192, 1024, 1) == (_lib.QF_PATH_GEMM, 8)     # 8 tiles: not 16 splits through global memory
+    assert _plan(16, 8192, 10240, 1) == (_lib.QF_PATH_GEMM, 3)    # 80 tiles
+    assert _plan(16, 4096, 18944, 1) == (_lib.QF_PATH_GEMM, 2)    # 148 tiles: two splits fill every slot
