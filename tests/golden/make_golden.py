@@ -1,7 +1,7 @@
 """Generate tests/golden/*.npz from the reference's own Python functions.
 
 Run in a container where the reference checkout is present:
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference      (or QF_REFERENCE_ROOT=/path/to/reference)
 It imports python/quantforge/baseline.py of the reference (pack_int4, unpack_int4,
 gemv_int4_baseline), runs them on seeded inputs on the CPU and stores inputs and
 outputs.  The fixtures are committed; the tests read only the .npz files.
@@ -14,7 +14,9 @@ import torch
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("QF_REFERENCE_ROOT")
+    if not ref_root:
+        raise SystemExit("usage: make_golden.py /path/to/reference  (the QuantForge checkout)")
     sys.path.insert(0, os.path.join(ref_root, "python"))
     from quantforge.baseline import gemv_int4_baseline, pack_int4, unpack_int4  # noqa: E402
 
