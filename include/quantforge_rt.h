@@ -137,6 +137,16 @@ int qf_w4a16_linear(qf_ctx *ctx, const qf_linear_desc *desc, const void *X, cons
 int qf_w4a16_linear_host(qf_ctx *ctx, const qf_linear_desc *desc, const void *X_host, const void *qweight,
                          const void *scales, const void *qzeros_or_null, void *Y_host, void *workspace,
                          size_t workspace_bytes, void *stream);
+/*
+ * The same without the final wait: the copies and the kernel are enqueued on `stream` and the call returns.
+ * Y_host holds the result once the caller has synchronised `stream`; X_host must stay unchanged until then.
+ * Use page-locked host buffers (with pageable ones the copies block the host anyway). Calls on one stream may be
+ * issued back to back: they share the context's staging buffers in stream order. Calls on different streams of
+ * one context must not overlap.
+ */
+int qf_w4a16_linear_host_async(qf_ctx *ctx, const qf_linear_desc *desc, const void *X_host, const void *qweight,
+                         const void *scales, const void *qzeros_or_null, void *Y_host, void *workspace,
+                         size_t workspace_bytes, void *stream);
 
 /*
  * One-time weight prepack: canonical -> QF_LAYOUT_INTERLEAVED (or back with to_canonical != 0).

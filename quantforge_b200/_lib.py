@@ -23,7 +23,7 @@ EXPORTS = [
     "qf_dequant_w4", "qf_w4a16_workspace_bytes", "qf_w4a16_linear", "qf_w4a16_linear_host", "qf_w4a16_plan",
     "qf_launch_count", "qf_prepack_w4", "qf_prepack_w4_tiled", "qf_w4a16_gemv_static_scratch", "qf_ctx_status", "qf_ctx_clear_status",
     "qf_comm_create", "qf_comm_export", "qf_comm_connect", "qf_comm_destroy", "qf_w4a16_linear_allreduce",
-    "qf_w4a16_linear_allgather",
+    "qf_w4a16_linear_allgather", "qf_w4a16_linear_host_async",
 ]
 QF_COMM_HANDLE_BYTES = 64
 
@@ -72,6 +72,7 @@ def load() -> ctypes.CDLL:
     lib.qf_w4a16_workspace_bytes.argtypes = [dp]
     lib.qf_w4a16_linear.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp, sz, vp]
     lib.qf_w4a16_linear_host.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.qf_w4a16_linear_host_async.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp, sz, vp]
     lib.qf_w4a16_gemv_static_scratch.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp]
     lib.qf_w4a16_plan.argtypes = [dp, ctypes.POINTER(i32), ctypes.POINTER(i32)]
     lib.qf_launch_count.restype = i64

@@ -344,7 +344,7 @@ static int grow(qf_ctx *ctx, void **buf, size_t *have, size_t need) {
     return QF_OK;
 }
 
-int qf_w4a16_linear_host(qf_ctx *ctx, const qf_linear_desc *desc, const void *X_host, const void *qweight,
+int qf_w4a16_linear_host_async(qf_ctx *ctx, const qf_linear_desc *desc, const void *X_host, const void *qweight,
                          const void *scales, const void *qzeros_or_null, void *Y_host, void *workspace,
                          size_t workspace_bytes, void *stream) {
     if (!ctx) return QF_ERR_BAD_ARG;
@@ -364,7 +364,16 @@ int qf_w4a16_linear_host(qf_ctx *ctx, const qf_linear_desc *desc, const void *X_
                          workspace_bytes, stream);
     if (st != QF_OK) return st;
     QF_CUDA_TRY(ctx, cudaMemcpyAsync(Y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, s));
-    QF_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+    return QF_OK;
+}
+
+int qf_w4a16_linear_host(qf_ctx *ctx, const qf_linear_desc *desc, const void *X_host, const void *qweight,
+                         const void *scales, const void *qzeros_or_null, void *Y_host, void *workspace,
+                         size_t workspace_bytes, void *stream) {
+    const int st = qf_w4a16_linear_host_async(ctx, desc, X_host, qweight, scales, qzeros_or_null, Y_host, workspace,
+                                              workspace_bytes, stream);
+    if (st != QF_OK) return st;
+    QF_CUDA_TRY(ctx, cudaStreamSynchronize((cudaStream_t)stream));
     return QF_OK;
 }
 

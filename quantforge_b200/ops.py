@@ -304,8 +304,12 @@ def w4a16_linear_allgather(x: torch.Tensor, qweight: torch.Tensor, scales: torch
 def w4a16_linear_host(x_host: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
                       zeros: Optional[torch.Tensor] = None, group_size: int = 128, zero_const: int = 8,
                       out_dtype: Optional[torch.dtype] = None, out_host: Optional[torch.Tensor] = None,
-                      path: int = QF_PATH_AUTO, weight_layout: int = QF_LAYOUT_CANONICAL) -> torch.Tensor:
-    """Same linear with activations and result in HOST memory (pinned for speed); weights stay on the GPU."""
+                      path: int = QF_PATH_AUTO, weight_layout: int = QF_LAYOUT_CANONICAL,
+                      wait: bool = True) -> torch.Tensor:
+    """Same linear with activations and result in HOST memory (pinned for speed); weights stay on the GPU.
+
+    wait=False enqueues the copies and the kernel on the current stream and returns at once: out_host is valid
+    after the stream has been synchronised (pinned buffers; x_host must not change until then)."""
     if x_host.is_cuda:
         raise ValueError("x_host must be a CPU tensor")
     dev = _need_cuda(qweight, scales, zeros)
@@ -318,9 +322,9 @@ def w4a16_linear_host(x_host: torch.Tensor, qweight: torch.Tensor, scales: torch
     ctx = _ctx(dev)
     with torch.cuda.device(dev):
         ws = _workspace(dev, workspace_bytes(d))
-        st = _lib.load().qf_w4a16_linear_host(ctx, ctypes.byref(d), _ptr(x_host), _ptr(qweight), _ptr(scales),
-                                              _ptr(zeros), _ptr(out_host), _ptr(ws),
-                                              ws.numel() if ws is not None else 0, _stream(dev))
+        fn = _lib.load().qf_w4a16_linear_host if wait else _lib.load().qf_w4a16_linear_host_async
+        st = fn(ctx, ctypes.byref(d), _ptr(x_host), _ptr(qweight), _ptr(scales), _ptr(zeros), _ptr(out_host),
+                _ptr(ws), ws.numel() if ws is not None else 0, _stream(dev))
     _check(st, ctx)
     return out_host
 
@@ -399,12 +403,16 @@ class W4A16Linear:
     """A quantised linear layer whose weights live on one GPU: y = x . W^T."""
 
     def __init__(self, qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor] = None,
-                 group_size: int = 128, zero_const: int = 8, prepack: bool = False):
+                 group_size: int = 128, zero_const: int = 8, prepack: bool = False,
+                 weight_layout: int = QF_LAYOUT_CANONICAL):
+        """weight_layout: the layout `qweight` is already in (weights that went through prepack_w4 before);
+        prepack=True converts canonical weights here instead."""
         _need_cuda(qweight, scales, zeros)
         self.qweight, self.scales, self.zeros = qweight.contiguous(), scales.contiguous(), zeros
         self.group_size, self.zero_const = group_size, zero_const
-        self.weight_layout = QF_LAYOUT_CANONICAL
-        if prepack and qweight.shape[0] % 128 == 0:
+        self.weight_layout = weight_layout
+        self._host_prep = {}
+        if prepack and weight_layout == QF_LAYOUT_CANONICAL and qweight.shape[0] % 128 == 0:
             self.qweight = prepack_w4(self.qweight, layout=QF_LAYOUT_TILED)
             self.weight_layout = QF_LAYOUT_TILED
         self.N = qweight.shape[0]
@@ -414,3 +422,33 @@ class W4A16Linear:
                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
         return w4a16_linear(x, self.qweight, self.scales, self.zeros, self.group_size, self.zero_const, out_dtype,
                             out=out, weight_layout=self.weight_layout)
+
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, wait: bool = True) -> torch.Tensor:
+        """Host activations in, host result out (both contiguous, ideally pinned), on the current stream of the
+        weights' device, which must be the current device. Descriptor, workspace and weight pointers are prepared
+        once per (batch, dtypes), so that a serving loop pays for little more than the C call.
+        wait=False: returns after enqueueing; out_host is valid once the stream has been synchronised."""
+        key = (x_host.shape[0], x_host.dtype, out_host.dtype)
+        prep = self._host_prep.get(key)
+        if prep is None:
+            if x_host.is_cuda or out_host.is_cuda:
+                raise ValueError("forward_host takes CPU tensors")
+            dev = self.qweight.device
+            M, N, K = _check_linear_tensors(x_host, self.qweight, self.scales, self.zeros, self.group_size)
+            d = _make_desc(M, N, K, self.group_size, x_host.dtype, out_host.dtype, self.zeros, self.zero_const,
+                           QF_PATH_AUTO, 0, self.weight_layout)
+            with torch.cuda.device(dev):
+                ws = _workspace(dev, workspace_bytes(d))
+            lib = _lib.load()
+            prep = (d, ctypes.byref(d), _ctx(dev), _ptr(self.qweight), _ptr(self.scales), _ptr(self.zeros), _ptr(ws),
+                    ws.numel() if ws is not None else 0, ws, (M, N), lib.qf_w4a16_linear_host,
+                    lib.qf_w4a16_linear_host_async, dev)
+            self._host_prep[key] = prep
+        d, dref, ctx, pw, ps, pz, pws, wsn, _ws, shape, fn_wait, fn_async, dev = prep
+        if tuple(out_host.shape) != shape or not out_host.is_contiguous() or not x_host.is_contiguous():
+            raise ValueError("x_host and out_host must be contiguous and out_host of shape [M, N]")
+        st = (fn_wait if wait else fn_async)(ctx, dref, x_host.data_ptr(), pw, ps, pz, out_host.data_ptr(), pws, wsn,
+                                             torch.cuda.current_stream(dev).cuda_stream)
+        if st != 0:
+            _check(st, ctx)
+        return out_host

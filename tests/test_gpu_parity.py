@@ -200,6 +200,40 @@ def test_host_entry_point(qf):
     assert O.rel_err(y.numpy(), want) < 1e-4
 
 
+def test_host_entry_point_async(qf):
+    """wait=False: several calls back to back on one stream, one synchronisation, same results as the waiting call."""
+    outs, wants = [], []
+    for seed, (M, K, N) in enumerate([(1, 1024, 512), (4, 2048, 256), (2, 512, 1024)]):
+        d = O.make_inputs(M=M, K=K, N=N, group_size=128, act_dtype="f16", seed=20 + seed)
+        x_host = torch.from_numpy(d["x"]).half().pin_memory()
+        args = (_t(d["qweight"]), _t(d["scales"], torch.float16), qf.pack_zeros_u4(_t(d["zeros"])))
+        wants.append(qf.w4a16_linear_host(x_host, *args, out_dtype=torch.float32).clone())
+        out = torch.empty(M, N, dtype=torch.float32).pin_memory()
+        outs.append((x_host, args, out))
+    for x_host, args, out in outs:
+        qf.w4a16_linear_host(x_host, *args, out_dtype=torch.float32, out_host=out, wait=False)
+    torch.cuda.synchronize()
+    for (_, _, out), want in zip(outs, wants):
+        assert torch.equal(out, want)
+
+
+def test_layer_object_host_path(qf):
+    """W4A16Linear.forward_host (prepared descriptors, waiting and not waiting) equals the plain device call."""
+    d = O.make_inputs(M=4, K=1024, N=512, group_size=128, act_dtype="bf16", seed=31)
+    qw, sc, zr = _t(d["qweight"]), _t(d["scales"], torch.bfloat16), qf.pack_zeros_u4(_t(d["zeros"]))
+    x_host = torch.from_numpy(d["x"]).to(torch.bfloat16).pin_memory()
+    want = qf.w4a16_linear(x_host.cuda(), qw, sc, zr, out_dtype=torch.float32).cpu()
+    for lin in (qf.W4A16Linear(qw, sc, zr), qf.W4A16Linear(qf.prepack_w4(qw), sc, zr, weight_layout=1)):
+        out = torch.empty(4, 512, dtype=torch.float32).pin_memory()
+        for wait in (True, False, False):
+            out.zero_()
+            lin.forward_host(x_host, out, wait=wait)
+            torch.cuda.synchronize()
+            assert O.rel_err(out.numpy(), want.numpy()) < 1e-5
+    with pytest.raises(ValueError):
+        lin.forward_host(x_host, torch.empty(3, 512, dtype=torch.float32))
+
+
 def test_error_behaviour(qf):
     from quantforge_b200 import QuantForgeError
     x = torch.zeros(1, 256, dtype=torch.float16, device="cuda")
