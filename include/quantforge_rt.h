@@ -181,6 +181,8 @@ int qf_ctx_clear_status(qf_ctx *ctx);
  * sums and arrival counters live in a scratch array that is part of the library image: a file-scope
  * `static __device__` array of QF_STATIC_SCRATCH_BYTES (16 MiB) that every GPU loading the library holds until
  * the process exits. The call issues no cudaMalloc / cudaFree and calls no allocating library routine.
+ * (Plans that sum their splits inside a thread-block cluster - 2..8 short splits - use no scratch at all; the
+ * array then only has its counters cleared.)
  *   - Limits: a linear whose plan needs more scratch than the array holds is refused with QF_ERR_WORKSPACE
  *     (the message names both sizes); use qf_w4a16_linear with your own workspace for those, or set
  *     desc.split_k = 1, which needs no scratch at all.
