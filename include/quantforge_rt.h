@@ -50,7 +50,8 @@ typedef enum qf_zero_mode { QF_ZERO_CONST = 0, QF_ZERO_U4 = 1, QF_ZERO_I8 = 2 } 
 
 /* Which kernel family serves a linear.  AUTO: M <= 2 -> GEMV kernel unless the weight matrix is large (32 MB
  * prepacked, 40 MB canonical), M >= 3 -> tcgen05 GEMM kernel (measured crossovers on B200); prepacked weights
- * and N % 128 != 0 override it, see qf_w4a16_plan. */
+ * (QF_LAYOUT_GEMV_SLAB always runs the streaming GEMV kernel, the other prepacked layouts the tcgen05 kernel),
+ * N % 128 != 0 and a fused epilogue override it, see qf_w4a16_plan. */
 typedef enum qf_path { QF_PATH_AUTO = 0, QF_PATH_GEMV = 1, QF_PATH_GEMM = 2 } qf_path;
 
 /*
@@ -63,12 +64,40 @@ typedef enum qf_path { QF_PATH_AUTO = 0, QF_PATH_GEMV = 1, QF_PATH_GEMM = 2 } qf
  *                           consumes per pipeline step are contiguous in HBM: word w (0..15) of row r (0..127) of
  *                           k-block kb of row tile nt sits at word index ((nt * K/128 + kb) * 128 + r) * 16 + w.
  *                           Needs N % 128 == 0. Produced once by qf_prepack_w4_tiled.
+ *   QF_LAYOUT_GEMV_SLAB   : one blob that holds codes, scales and zeros in the order the streaming GEMV kernel
+ *                           consumes them, so that every thread block reads ONE contiguous range of HBM with bulk
+ *                           copies. Unit u = b * (K/128) + c covers weight rows [64b, 64b+64) x codes [128c, 128c+128)
+ *                           and is QF_SLAB_UNIT_BYTES long: four tiles (16 rows each) of
+ *                             512 B  rows r = 0..7 : lane (r, t) owns the interleaved words t, t+4, t+8, t+12 of the chunk
+ *                             512 B  rows r + 8    : same
+ *                              64 B  per row: 16-bit converter constant (magic + zero point) | 16-bit scale << 16
+ *                           `qweight` of the linear calls points to the blob; `scales` and `qzeros` are ignored (may be
+ *                           NULL). The blob is specific to (group_size, act_dtype, zero mode) of the descriptor it was
+ *                           built with. Needs N % 64 == 0; serves M <= QF_SLAB_MAX_M. Produced by qf_prepack_gemv_slab.
  */
 typedef enum qf_weight_layout {
     QF_LAYOUT_CANONICAL = 0,
     QF_LAYOUT_INTERLEAVED = 1,
-    QF_LAYOUT_TILED = 2
+    QF_LAYOUT_TILED = 2,
+    QF_LAYOUT_GEMV_SLAB = 3
 } qf_weight_layout;
+#define QF_SLAB_UNIT_BYTES 4352
+#define QF_SLAB_MAX_M 32
+
+/*
+ * Work fused behind the contraction (no counterpart in the reference, whose furthest fusion is unpack + dequant,
+ * lib/Transforms/FuseUnpackDequant.cpp:68-305; these remove the elementwise kernels that follow the linears of a
+ * decoder layer).
+ *   QF_EPI_SILU_MUL     : gate and up projections as ONE linear whose weight rows alternate in groups of 8:
+ *                         rows [16j, 16j+8) = gate rows [8j, 8j+8), rows [16j+8, 16j+16) = up rows [8j, 8j+8)
+ *                         (scales and zeros permuted alike); desc.N counts both (a multiple of 16). The kernel
+ *                         writes Y[M, N/2] = silu(gate) * up, silu(v) = v / (1 + exp(-v)), evaluated in fp32 on the
+ *                         fp32 accumulators and rounded once.
+ *   QF_EPI_RESIDUAL_ADD : Y[M, N] = X . W^T + R, R [M, N] in out_dtype (the `residual` argument of
+ *                         qf_w4a16_linear_fused; R may alias Y), added in fp32 before the one rounding.
+ * Served by the streaming GEMV kernel (QF_LAYOUT_GEMV_SLAB) and by the tcgen05 kernel.
+ */
+typedef enum qf_epilogue { QF_EPI_NONE = 0, QF_EPI_SILU_MUL = 1, QF_EPI_RESIDUAL_ADD = 2 } qf_epilogue;
 
 typedef struct qf_ctx qf_ctx;
 
@@ -80,9 +109,12 @@ typedef struct qf_linear_desc {
     int32_t zero_mode;   /* qf_zero_mode */
     int32_t zero_const;  /* used when zero_mode == QF_ZERO_CONST (8 = symmetric int4, 0 = the zp==0 fast path) */
     int32_t path;        /* qf_path */
-    int32_t split_k;     /* 0 = heuristic; >0 forces the number of K splits */
+    int32_t split_k;     /* 0 = heuristic; >0 requests a number of K splits (clamped to what the kernel can run;
+                            qf_w4a16_plan reports the split in use). With QF_LAYOUT_GEMV_SLAB: the number of
+                            thread blocks the weight stream is divided among (0 = a multiple of the SM count). */
     int32_t weight_layout; /* qf_weight_layout of qweight */
-    int32_t reserved[4]; /* must be zero */
+    int32_t epilogue;    /* qf_epilogue */
+    int32_t reserved[3]; /* must be zero */
 } qf_linear_desc;
 
 int qf_version(void);
@@ -129,6 +161,27 @@ int qf_w4a16_linear(qf_ctx *ctx, const qf_linear_desc *desc, const void *X, cons
                     const void *qzeros_or_null, void *Y, void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * The linear with a fused epilogue (desc->epilogue, see qf_epilogue). `residual` is read only by
+ * QF_EPI_RESIDUAL_ADD and may be NULL otherwise. With QF_EPI_NONE this is qf_w4a16_linear.
+ */
+int qf_w4a16_linear_fused(qf_ctx *ctx, const qf_linear_desc *desc, const void *X, const void *qweight,
+                          const void *scales, const void *qzeros_or_null, void *Y, const void *residual,
+                          void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * `count` linears enqueued back to back on `stream` by one call (the linears of a decoder layer: q/k/v as one
+ * concatenated linear, o with the residual, gate/up with SiLU * mul, down with the residual). Entry i uses
+ * descs[i], X[i], qweight[i], scales[i], qzeros[i] (may be NULL), Y[i], residual[i] (`residual` itself may be
+ * NULL). Consecutive kernels are chained with programmatic dependent launch, so entry i+1 may read what entry i
+ * wrote. `workspace` must hold the largest qf_w4a16_workspace_bytes over the entries. Stops at the first entry
+ * that fails and returns its status (earlier entries stay enqueued).
+ */
+int qf_w4a16_linear_batched(qf_ctx *ctx, int count, const qf_linear_desc *descs, const void *const *X,
+                            const void *const *qweight, const void *const *scales, const void *const *qzeros,
+                            void *const *Y, const void *const *residual, void *workspace, size_t workspace_bytes,
+                            void *stream);
+
+/*
  * The same linear for callers that hold activations in HOST memory (the reference's Python entry
  * point takes CPU tensors when no GPU is used): copies X_host to the device, runs the kernel,
  * copies Y back and waits.  Weights, scales and zeros stay DEVICE pointers (they are loaded once).
@@ -161,6 +214,36 @@ int qf_prepack_w4_tiled(qf_ctx *ctx, const void *qweight_in, void *qweight_out, 
                         int to_canonical, void *stream);
 
 /*
+ * Bytes of a weight tensor of N rows x K codes in `layout`: N*K/2 for the canonical, interleaved and tiled layouts
+ * (pure permutations), (N/64)*(K/128)*QF_SLAB_UNIT_BYTES for QF_LAYOUT_GEMV_SLAB (scales and zeros included).
+ * 0 when the layout does not admit the shape.
+ */
+size_t qf_prepack_bytes(int layout, int64_t N, int64_t K);
+
+/*
+ * One-time prepack for the streaming GEMV kernel: canonical qweight + scales + zeros -> one QF_LAYOUT_GEMV_SLAB
+ * blob of qf_prepack_bytes(QF_LAYOUT_GEMV_SLAB, N, K) bytes (16-byte aligned, must not alias the inputs).
+ * Uses N, K, group_size, act_dtype, zero_mode, zero_const of `desc`. No reference counterpart (see qf_prepack_w4).
+ * qf_unpack_gemv_slab writes the codes of a blob back as canonical qweight [N, K/2]: the inverse permutation,
+ * there so that prepacking can be checked bit for bit.
+ */
+int qf_prepack_gemv_slab(qf_ctx *ctx, const qf_linear_desc *desc, const void *qweight, const void *scales,
+                         const void *qzeros_or_null, void *blob_out, void *stream);
+int qf_unpack_gemv_slab(qf_ctx *ctx, int64_t N, int64_t K, const void *blob, void *qweight_out, void *stream);
+
+/*
+ * Weight orientation of the reference's compiler half: its matcher puts the quantised operand of linalg.matmul
+ * as W[K, N] (lib/Transforms/ConvertLinalgToQuantForge.cpp:185-203) and its tests pack two codes per byte along
+ * the LAST dim, i.e. along N (test/Transforms/lower_unpack_to_arith.mlir:31-35). The kernels contract over rows
+ * packed along K (python/quantforge/baseline.py:58-71). This converts once, on the device:
+ *   packed_along_n = 0 : w_kn is int8[K, N], one code (0..15, upper bits ignored) per byte
+ *   packed_along_n = 1 : w_kn is int8[K, N/2], byte j of row k = code[k, 2j] | code[k, 2j+1] << 4
+ * -> qweight_out int8[N, K/2] canonical. K % 8 == 0, N % 2 == 0.
+ */
+int qf_repack_kn_to_canonical(qf_ctx *ctx, const void *w_kn, int packed_along_n, int64_t K, int64_t N,
+                              void *qweight_out, void *stream);
+
+/*
  * Sticky device-side status of this context: QF_OK, or QF_ERR_TIMEOUT when a kernel's bounded wait expired
  * (the kernel then returned without finishing its tile). Reading it does not synchronise; call it after the
  * stream has been synchronised. qf_ctx_clear_status resets it.
@@ -184,8 +267,9 @@ int qf_ctx_clear_status(qf_ctx *ctx);
  * (Plans that sum their splits inside a thread-block cluster - 2..8 short splits - use no scratch at all; the
  * array then only has its counters cleared.)
  *   - Limits: a linear whose plan needs more scratch than the array holds is refused with QF_ERR_WORKSPACE
- *     (the message names both sizes); use qf_w4a16_linear with your own workspace for those, or set
- *     desc.split_k = 1, which needs no scratch at all.
+ *     (the message names both sizes); use qf_w4a16_linear with your own workspace for those. For K <= 4096
+ *     desc.split_k = 1 is a plan without any scratch; longer K is always split (a split covers at most 4096
+ *     codes), so the request is clamped, see qf_w4a16_plan.
  *   - The array is shared by every call on that device and keeps the previous call's contents. The counters a
  *     call uses are cleared on `stream` before the kernel starts; the partial sums are fully overwritten before
  *     they are read. Two calls that overlap in time on one device (different streams, or different host threads)

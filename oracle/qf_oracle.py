@@ -173,6 +173,32 @@ def w4a16_linear(x: np.ndarray, qweight: np.ndarray, scales: np.ndarray, zeros, 
     return round_to(y, out_dtype)
 
 
+# --------------------------------------------------------------------------- #
+# what follows the linear inside a decoder layer (no reference counterpart: definitions for the fused epilogues)
+# --------------------------------------------------------------------------- #
+def interleave8(a: np.ndarray, b: np.ndarray, axis: int = 0) -> np.ndarray:
+    """Groups of 8 entries of `a` followed by the matching 8 of `b`, along `axis` (the gate|up row order)."""
+    a = np.moveaxis(np.asarray(a), axis, 0)
+    b = np.moveaxis(np.asarray(b), axis, 0)
+    n = a.shape[0]
+    assert a.shape == b.shape and n % 8 == 0
+    both = np.stack([a.reshape(n // 8, 8, *a.shape[1:]), b.reshape(n // 8, 8, *b.shape[1:])], axis=1)
+    return np.ascontiguousarray(np.moveaxis(both.reshape(2 * n, *a.shape[1:]), 0, axis))
+
+
+def silu_mul(gate: np.ndarray, up: np.ndarray, out_dtype: str = F32) -> np.ndarray:
+    """silu(gate) * up on fp32 accumulators, rounded once: silu(v) = v / (1 + exp(-v))."""
+    g = np.asarray(gate, dtype=np.float64)
+    u = np.asarray(up, dtype=np.float64)
+    return round_to((g / (1.0 + np.exp(-g)) * u).astype(np.float32), out_dtype)
+
+
+def repack_kn_to_canonical(codes_kn: np.ndarray) -> np.ndarray:
+    """codes int8[K, N] (the matmul operand orientation of lib/Transforms/ConvertLinalgToQuantForge.cpp:185-203)
+    -> canonical int8[N, K/2] packed along K (python/quantforge/baseline.py:58-71)."""
+    return pack_int4(np.ascontiguousarray(np.asarray(codes_kn, dtype=np.int8).T))
+
+
 def gemv_int4_per_channel(x: np.ndarray, w_packed: np.ndarray, scale: np.ndarray,
                           zero_point: np.ndarray) -> np.ndarray:
     """Restatement of python/quantforge/baseline.py:52-72 (f16 everywhere, per-row scale/zp).

@@ -15,7 +15,10 @@ QF_OK = 0
 QF_F16, QF_BF16, QF_F32 = 0, 1, 2
 QF_ZERO_CONST, QF_ZERO_U4, QF_ZERO_I8 = 0, 1, 2
 QF_PATH_AUTO, QF_PATH_GEMV, QF_PATH_GEMM = 0, 1, 2
-QF_LAYOUT_CANONICAL, QF_LAYOUT_INTERLEAVED, QF_LAYOUT_TILED = 0, 1, 2
+QF_LAYOUT_CANONICAL, QF_LAYOUT_INTERLEAVED, QF_LAYOUT_TILED, QF_LAYOUT_GEMV_SLAB = 0, 1, 2, 3
+QF_EPI_NONE, QF_EPI_SILU_MUL, QF_EPI_RESIDUAL_ADD = 0, 1, 2
+QF_SLAB_UNIT_BYTES = 4352
+QF_SLAB_MAX_M = 32
 
 # every symbol include/quantforge_rt.h declares
 EXPORTS = [
@@ -23,7 +26,8 @@ EXPORTS = [
     "qf_dequant_w4", "qf_w4a16_workspace_bytes", "qf_w4a16_linear", "qf_w4a16_linear_host", "qf_w4a16_plan",
     "qf_launch_count", "qf_prepack_w4", "qf_prepack_w4_tiled", "qf_w4a16_gemv_static_scratch", "qf_ctx_status", "qf_ctx_clear_status",
     "qf_comm_create", "qf_comm_export", "qf_comm_connect", "qf_comm_destroy", "qf_w4a16_linear_allreduce",
-    "qf_w4a16_linear_allgather", "qf_w4a16_linear_host_async",
+    "qf_w4a16_linear_allgather", "qf_w4a16_linear_host_async", "qf_w4a16_linear_fused", "qf_w4a16_linear_batched",
+    "qf_prepack_bytes", "qf_prepack_gemv_slab", "qf_unpack_gemv_slab", "qf_repack_kn_to_canonical",
 ]
 QF_COMM_HANDLE_BYTES = 64
 
@@ -33,7 +37,8 @@ class LinearDesc(ctypes.Structure):
         ("M", ctypes.c_int64), ("N", ctypes.c_int64), ("K", ctypes.c_int64),
         ("group_size", ctypes.c_int32), ("act_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
         ("zero_mode", ctypes.c_int32), ("zero_const", ctypes.c_int32), ("path", ctypes.c_int32),
-        ("split_k", ctypes.c_int32), ("weight_layout", ctypes.c_int32), ("reserved", ctypes.c_int32 * 4),
+        ("split_k", ctypes.c_int32), ("weight_layout", ctypes.c_int32), ("epilogue", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 3),
     ]
 
 
@@ -71,6 +76,14 @@ def load() -> ctypes.CDLL:
     lib.qf_w4a16_workspace_bytes.restype = sz
     lib.qf_w4a16_workspace_bytes.argtypes = [dp]
     lib.qf_w4a16_linear.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.qf_w4a16_linear_fused.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
+    pvp = ctypes.POINTER(vp)
+    lib.qf_w4a16_linear_batched.argtypes = [vp, ctypes.c_int, dp, pvp, pvp, pvp, pvp, pvp, pvp, vp, sz, vp]
+    lib.qf_prepack_bytes.restype = sz
+    lib.qf_prepack_bytes.argtypes = [ctypes.c_int, i64, i64]
+    lib.qf_prepack_gemv_slab.argtypes = [vp, dp, vp, vp, vp, vp, vp]
+    lib.qf_unpack_gemv_slab.argtypes = [vp, i64, i64, vp, vp, vp]
+    lib.qf_repack_kn_to_canonical.argtypes = [vp, vp, ctypes.c_int, i64, i64, vp, vp]
     lib.qf_w4a16_linear_host.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp, sz, vp]
     lib.qf_w4a16_linear_host_async.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp, sz, vp]
     lib.qf_w4a16_gemv_static_scratch.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp]

@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libquantforge_rt.so")
 
-SOURCES = ["qf_api.cu", "qf_unpack.cu", "qf_gemv.cu", "qf_gemm_tcgen05.cu", "qf_comm.cu"]
+SOURCES = ["qf_api.cu", "qf_unpack.cu", "qf_gemv.cu", "qf_gemv_slab.cu", "qf_gemm_tcgen05.cu", "qf_comm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",

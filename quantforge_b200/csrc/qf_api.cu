@@ -54,10 +54,31 @@ int make_plan(const qf_linear_desc *d, Plan *p, std::string *why) {
         return bad(QF_ERR_BAD_ARG, "zero_const must fit a signed 8-bit zero point");
     if (d->split_k < 0) return bad(QF_ERR_BAD_ARG, "split_k must be >= 0");
     if (d->weight_layout != QF_LAYOUT_CANONICAL && d->weight_layout != QF_LAYOUT_INTERLEAVED &&
-        d->weight_layout != QF_LAYOUT_TILED)
+        d->weight_layout != QF_LAYOUT_TILED && d->weight_layout != QF_LAYOUT_GEMV_SLAB)
         return bad(QF_ERR_BAD_ARG, "unknown weight_layout");
-    for (int i = 0; i < 4; ++i)
+    if (d->epilogue != QF_EPI_NONE && d->epilogue != QF_EPI_SILU_MUL && d->epilogue != QF_EPI_RESIDUAL_ADD)
+        return bad(QF_ERR_BAD_ARG, "unknown epilogue");
+    for (int i = 0; i < 3; ++i)
         if (d->reserved[i] != 0) return bad(QF_ERR_BAD_ARG, "reserved fields must be zero");
+    p->slab = false;
+    if (d->weight_layout == QF_LAYOUT_GEMV_SLAB) {
+        if (d->path == QF_PATH_GEMM)
+            return bad(QF_ERR_BAD_ARG, "QF_LAYOUT_GEMV_SLAB weights are read by the GEMV path only");
+        if (d->N % 64 != 0) return bad(QF_ERR_BAD_ARG, "QF_LAYOUT_GEMV_SLAB needs N to be a multiple of 64");
+        if (d->M > QF_SLAB_MAX_M)
+            return bad(QF_ERR_UNSUPPORTED, "QF_LAYOUT_GEMV_SLAB serves M <= 32; use a tcgen05 layout for larger batches");
+        int grid = 1, depth = 1;
+        slab_geometry(d->M, d->N, d->K, kSmCount, d->split_k, &grid, &depth);
+        p->slab = true;
+        p->path = QF_PATH_GEMV;
+        p->split_k = grid;
+        p->chunks_per_split = depth;
+        p->m_tiles = 1;
+        p->bn = 8 * ((slab_m_pad(d->M) + 7) / 8);
+        p->ws_partial_bytes = slab_workspace_bytes(grid, d->M);
+        p->ws_counter_bytes = 0;
+        return QF_OK;
+    }
 
     int path = d->path;
     if (path == QF_PATH_AUTO) {
@@ -70,6 +91,13 @@ int make_plan(const qf_linear_desc *d, Plan *p, std::string *why) {
         path = (d->M <= 2 && !big) ? QF_PATH_GEMV : QF_PATH_GEMM;
     }
     if (path != QF_PATH_GEMV && path != QF_PATH_GEMM) return bad(QF_ERR_BAD_ARG, "unknown path");
+    if (d->epilogue != QF_EPI_NONE) {
+        // the fused epilogues live in the streaming GEMV kernel (above) and in the tcgen05 kernel
+        if (d->path == QF_PATH_GEMV || d->N % 128 != 0)
+            return bad(QF_ERR_UNSUPPORTED,
+                       "a fused epilogue needs QF_LAYOUT_GEMV_SLAB weights or the tcgen05 path (N % 128 == 0)");
+        path = QF_PATH_GEMM;
+    }
     if (path == QF_PATH_GEMM && d->N % 128 != 0) {
         if (d->path == QF_PATH_GEMM) return bad(QF_ERR_BAD_ARG, "the GEMM path needs N to be a multiple of 128");
         path = QF_PATH_GEMV;
@@ -176,6 +204,13 @@ int make_plan(const qf_linear_desc *d, Plan *p, std::string *why) {
 static int check_linear_args(qf_ctx *ctx, const qf_linear_desc *d, const void *X, const void *qw, const void *scales,
                              const void *zeros, const void *Y) {
     if (!ctx) return QF_ERR_BAD_ARG;
+    if (d->weight_layout == QF_LAYOUT_GEMV_SLAB) {
+        // the blob carries scales and zeros
+        if (!X || !qw || !Y) return fail(ctx, QF_ERR_BAD_ARG, "null tensor pointer");
+        if (!aligned16(X) || !aligned16(qw) || !aligned16(Y))
+            return fail(ctx, QF_ERR_BAD_ARG, "device pointers must be 16-byte aligned");
+        return QF_OK;
+    }
     if (!X || !qw || !scales || !Y) return fail(ctx, QF_ERR_BAD_ARG, "null tensor pointer");
     if (d->zero_mode != QF_ZERO_CONST && !zeros) return fail(ctx, QF_ERR_BAD_ARG, "zero_mode needs a qzeros tensor");
     if (d->zero_mode == QF_ZERO_U4 && d->N % 8 != 0) return fail(ctx, QF_ERR_BAD_ARG, "QF_ZERO_U4 needs N % 8 == 0");
@@ -213,7 +248,8 @@ int qf_ctx_create(qf_ctx **out, int device) {
     cudaError_t e = cudaGetDeviceCount(&count);
     if (e != cudaSuccess || count == 0) return QF_ERR_CUDA;  // no CPU fallback exists
     if (device < 0 || device >= count) return QF_ERR_BAD_ARG;
-    if (cudaSetDevice(device) != cudaSuccess) return QF_ERR_CUDA;
+    DeviceGuard guard(device);  // the caller's current device is restored on every return path
+    if (!guard.ok()) return QF_ERR_CUDA;
     qf_ctx *ctx = new (std::nothrow) qf_ctx();
     if (!ctx) return QF_ERR_CUDA;
     ctx->device = device;
@@ -229,6 +265,7 @@ int qf_ctx_create(qf_ctx **out, int device) {
     }
     int st = gemv_init(ctx);
     if (st == QF_OK) st = gemm_init(ctx);
+    if (st == QF_OK) st = gemv_slab_init(ctx);
     if (st != QF_OK) {
         delete ctx;
         return st;
@@ -239,7 +276,7 @@ int qf_ctx_create(qf_ctx **out, int device) {
 
 int qf_ctx_destroy(qf_ctx *ctx) {
     if (!ctx) return QF_OK;
-    cudaSetDevice(ctx->device);
+    DeviceGuard guard(ctx->device);
     if (ctx->stage_x) cudaFree(ctx->stage_x);
     if (ctx->stage_y) cudaFree(ctx->stage_y);
     if (ctx->host_status) cudaFreeHost(ctx->host_status);
@@ -262,10 +299,13 @@ int qf_dequant_w4(qf_ctx *ctx, const qf_linear_desc *desc, const void *qweight, 
                   const void *qzeros_or_null, void *w_out, void *stream) {
     if (!ctx) return QF_ERR_BAD_ARG;
     if (!desc) return fail(ctx, QF_ERR_BAD_ARG, "desc is null");
+    if (desc->weight_layout != QF_LAYOUT_CANONICAL)
+        return fail(ctx, QF_ERR_UNSUPPORTED, "qf_dequant_w4 reads canonical weights only (undo the prepack first)");
     qf_linear_desc d = *desc;
     d.M = 1;
     d.path = QF_PATH_GEMV;
     d.out_dtype = d.act_dtype;
+    d.epilogue = QF_EPI_NONE;
     Plan plan;
     std::string why;
     int st = make_plan(&d, &plan, &why);
@@ -290,8 +330,9 @@ int qf_w4a16_plan(const qf_linear_desc *desc, int32_t *path_out, int32_t *split_
     return QF_OK;
 }
 
-int qf_w4a16_linear(qf_ctx *ctx, const qf_linear_desc *desc, const void *X, const void *qweight, const void *scales,
-                    const void *qzeros_or_null, void *Y, void *workspace, size_t workspace_bytes, void *stream) {
+int qf_w4a16_linear_fused(qf_ctx *ctx, const qf_linear_desc *desc, const void *X, const void *qweight,
+                          const void *scales, const void *qzeros_or_null, void *Y, const void *residual,
+                          void *workspace, size_t workspace_bytes, void *stream) {
     if (!ctx) return QF_ERR_BAD_ARG;
     Plan plan;
     std::string why;
@@ -300,15 +341,111 @@ int qf_w4a16_linear(qf_ctx *ctx, const qf_linear_desc *desc, const void *X, cons
     if (desc->M == 0) return QF_OK;
     st = check_linear_args(ctx, desc, X, qweight, scales, qzeros_or_null, Y);
     if (st != QF_OK) return st;
+    st = check_current_device(ctx);
+    if (st != QF_OK) return st;
+    if (desc->epilogue == QF_EPI_RESIDUAL_ADD && (!residual || !aligned16(residual)))
+        return fail(ctx, QF_ERR_BAD_ARG, "QF_EPI_RESIDUAL_ADD needs a 16-byte aligned residual tensor");
+    if (desc->epilogue == QF_EPI_SILU_MUL && desc->N % 16 != 0)
+        return fail(ctx, QF_ERR_BAD_ARG, "QF_EPI_SILU_MUL needs N (gate and up rows together) to be a multiple of 16");
     const size_t need = plan.ws_partial_bytes + plan.ws_counter_bytes;
     if (need > 0) {
         if (!workspace || workspace_bytes < need)
             return fail(ctx, QF_ERR_WORKSPACE, "workspace smaller than qf_w4a16_workspace_bytes(desc)");
         if (!aligned16(workspace)) return fail(ctx, QF_ERR_BAD_ARG, "workspace must be 16-byte aligned");
     }
+    if (plan.slab)
+        return launch_gemv_slab(ctx, desc, plan, X, qweight, Y, residual, workspace, (cudaStream_t)stream);
     if (plan.path == QF_PATH_GEMV)
         return launch_gemv(ctx, desc, plan, X, qweight, scales, qzeros_or_null, Y, workspace, (cudaStream_t)stream);
-    return launch_gemm(ctx, desc, plan, X, qweight, scales, qzeros_or_null, Y, workspace, (cudaStream_t)stream);
+    return launch_gemm(ctx, desc, plan, X, qweight, scales, qzeros_or_null, Y, residual, workspace,
+                       (cudaStream_t)stream);
+}
+
+int qf_w4a16_linear(qf_ctx *ctx, const qf_linear_desc *desc, const void *X, const void *qweight, const void *scales,
+                    const void *qzeros_or_null, void *Y, void *workspace, size_t workspace_bytes, void *stream) {
+    if (desc && desc->epilogue == QF_EPI_RESIDUAL_ADD)
+        return fail(ctx, QF_ERR_BAD_ARG, "QF_EPI_RESIDUAL_ADD takes its residual through qf_w4a16_linear_fused");
+    return qf_w4a16_linear_fused(ctx, desc, X, qweight, scales, qzeros_or_null, Y, nullptr, workspace, workspace_bytes,
+                                 stream);
+}
+
+int qf_w4a16_linear_batched(qf_ctx *ctx, int count, const qf_linear_desc *descs, const void *const *X,
+                            const void *const *qweight, const void *const *scales, const void *const *qzeros,
+                            void *const *Y, const void *const *residual, void *workspace, size_t workspace_bytes,
+                            void *stream) {
+    if (!ctx) return QF_ERR_BAD_ARG;
+    if (count < 0) return fail(ctx, QF_ERR_BAD_ARG, "negative count");
+    if (count == 0) return QF_OK;
+    if (!descs || !X || !qweight || !Y) return fail(ctx, QF_ERR_BAD_ARG, "null argument array");
+    for (int i = 0; i < count; ++i) {
+        const int st = qf_w4a16_linear_fused(ctx, &descs[i], X[i], qweight[i], scales ? scales[i] : nullptr,
+                                             qzeros ? qzeros[i] : nullptr, Y[i], residual ? residual[i] : nullptr,
+                                             workspace, workspace_bytes, stream);
+        if (st != QF_OK) {
+            ctx->last_error = "entry " + std::to_string(i) + ": " + ctx->last_error;
+            return st;
+        }
+    }
+    return QF_OK;
+}
+
+size_t qf_prepack_bytes(int layout, int64_t N, int64_t K) {
+    if (N <= 0 || K <= 0 || K % 128 != 0) return 0;
+    switch (layout) {
+        case QF_LAYOUT_CANONICAL: return (size_t)N * (size_t)K / 2;
+        case QF_LAYOUT_INTERLEAVED:
+        case QF_LAYOUT_TILED: return N % 128 == 0 ? (size_t)N * (size_t)K / 2 : 0;
+        case QF_LAYOUT_GEMV_SLAB: return N % 64 == 0 ? (size_t)(N / 64) * (size_t)(K / 128) * QF_SLAB_UNIT_BYTES : 0;
+        default: return 0;
+    }
+}
+
+int qf_prepack_gemv_slab(qf_ctx *ctx, const qf_linear_desc *desc, const void *qweight, const void *scales,
+                         const void *qzeros_or_null, void *blob_out, void *stream) {
+    if (!ctx) return QF_ERR_BAD_ARG;
+    if (!desc) return fail(ctx, QF_ERR_BAD_ARG, "desc is null");
+    qf_linear_desc d = *desc;
+    d.M = 1;
+    d.path = QF_PATH_AUTO;
+    d.weight_layout = QF_LAYOUT_GEMV_SLAB;
+    d.epilogue = QF_EPI_NONE;
+    d.out_dtype = d.act_dtype;
+    Plan plan;
+    std::string why;
+    int st = make_plan(&d, &plan, &why);
+    if (st != QF_OK) return fail(ctx, st, why);
+    if (!qweight || !scales || !blob_out) return fail(ctx, QF_ERR_BAD_ARG, "null tensor pointer");
+    if (d.zero_mode != QF_ZERO_CONST && !qzeros_or_null) return fail(ctx, QF_ERR_BAD_ARG, "zero_mode needs a qzeros tensor");
+    if (!aligned16(qweight) || !aligned16(scales) || !aligned16(blob_out) || (qzeros_or_null && !aligned16(qzeros_or_null)))
+        return fail(ctx, QF_ERR_BAD_ARG, "device pointers must be 16-byte aligned");
+    if (blob_out == qweight) return fail(ctx, QF_ERR_BAD_ARG, "the blob must not alias the canonical weights");
+    st = check_current_device(ctx);
+    if (st != QF_OK) return st;
+    return launch_slab_prepack(ctx, &d, qweight, scales, qzeros_or_null, blob_out, (cudaStream_t)stream);
+}
+
+int qf_unpack_gemv_slab(qf_ctx *ctx, int64_t N, int64_t K, const void *blob, void *qweight_out, void *stream) {
+    if (!ctx) return QF_ERR_BAD_ARG;
+    if (N <= 0 || K <= 0 || N % 64 != 0 || K % 128 != 0)
+        return fail(ctx, QF_ERR_BAD_ARG, "QF_LAYOUT_GEMV_SLAB needs N % 64 == 0 and K % 128 == 0");
+    if (!blob || !qweight_out) return fail(ctx, QF_ERR_BAD_ARG, "null tensor pointer");
+    if (!aligned16(blob) || !aligned16(qweight_out)) return fail(ctx, QF_ERR_BAD_ARG, "device pointers must be 16-byte aligned");
+    int st = check_current_device(ctx);
+    if (st != QF_OK) return st;
+    return launch_slab_unpack(ctx, N, K, blob, qweight_out, (cudaStream_t)stream);
+}
+
+int qf_repack_kn_to_canonical(qf_ctx *ctx, const void *w_kn, int packed_along_n, int64_t K, int64_t N,
+                              void *qweight_out, void *stream) {
+    if (!ctx) return QF_ERR_BAD_ARG;
+    if (K <= 0 || N <= 0 || K % 8 != 0 || N % 2 != 0)
+        return fail(ctx, QF_ERR_BAD_ARG, "qf_repack_kn_to_canonical needs K % 8 == 0 and N % 2 == 0");
+    if (!w_kn || !qweight_out) return fail(ctx, QF_ERR_BAD_ARG, "null tensor pointer");
+    if (w_kn == qweight_out) return fail(ctx, QF_ERR_BAD_ARG, "in and out must not alias");
+    if (((uintptr_t)qweight_out & 3u) != 0) return fail(ctx, QF_ERR_BAD_ARG, "output must be 4-byte aligned");
+    int st = check_current_device(ctx);
+    if (st != QF_OK) return st;
+    return launch_repack_kn(ctx, w_kn, packed_along_n ? 1 : 0, K, N, qweight_out, (cudaStream_t)stream);
 }
 
 int qf_w4a16_gemv_static_scratch(qf_ctx *ctx, const qf_linear_desc *desc, const void *X, const void *qweight,

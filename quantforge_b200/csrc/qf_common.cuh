@@ -94,6 +94,29 @@ inline cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, di
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+// Makes `device` current for the lifetime of the object and restores the caller's device afterwards.
+class DeviceGuard {
+  public:
+    explicit DeviceGuard(int device) {
+        ok_ = cudaGetDevice(&prev_) == cudaSuccess;
+        if (ok_ && prev_ != device) {
+            ok_ = cudaSetDevice(device) == cudaSuccess;
+            switched_ = ok_;
+        }
+    }
+    ~DeviceGuard() {
+        if (switched_) cudaSetDevice(prev_);
+    }
+    bool ok() const { return ok_; }
+    DeviceGuard(const DeviceGuard &) = delete;
+    DeviceGuard &operator=(const DeviceGuard &) = delete;
+
+  private:
+    int prev_ = -1;
+    bool ok_ = false;
+    bool switched_ = false;
+};
+
 inline int fail(qf_ctx *ctx, int status, const std::string &msg) {
     if (ctx) ctx->last_error = msg;
     return status;
@@ -101,6 +124,16 @@ inline int fail(qf_ctx *ctx, int status, const std::string &msg) {
 
 inline int cuda_fail(qf_ctx *ctx, cudaError_t e, const char *what) {
     return fail(ctx, QF_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+// The compute entry points launch on the current device: it must be the context's.
+inline int check_current_device(qf_ctx *ctx) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return fail(ctx, QF_ERR_CUDA, "cudaGetDevice failed");
+    if (dev != ctx->device)
+        return fail(ctx, QF_ERR_BAD_ARG, "the current CUDA device (" + std::to_string(dev) +
+                                             ") is not the context's device (" + std::to_string(ctx->device) + ")");
+    return QF_OK;
 }
 
 #define QF_CUDA_TRY(ctx, expr)                                   \
@@ -111,8 +144,9 @@ inline int cuda_fail(qf_ctx *ctx, cudaError_t e, const char *what) {
 
 struct Plan {
     int path;            // QF_PATH_GEMV / QF_PATH_GEMM
-    int split_k;         // number of K splits
-    int chunks_per_split;  // GEMV: 128-code chunks per split; GEMM: k-blocks per split
+    int split_k;         // number of K splits (slab GEMV: thread blocks of the launch)
+    int chunks_per_split;  // GEMV: 128-code chunks per split; GEMM: k-blocks per split; slab GEMV: ring depth
+    bool slab;           // QF_LAYOUT_GEMV_SLAB weights: the streaming GEMV kernel
     int m_tiles;         // GEMV: ceil(M/8); GEMM: batch tiles
     int bn;              // GEMM: batch tile width (MMA N)
     size_t ws_partial_bytes;
@@ -159,7 +193,7 @@ int launch_dequant(qf_ctx *ctx, const qf_linear_desc *d, const void *qw, const v
 int launch_gemv(qf_ctx *ctx, const qf_linear_desc *d, const Plan &p, const void *X, const void *qw,
                 const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s);
 int launch_gemm(qf_ctx *ctx, const qf_linear_desc *d, const Plan &p, const void *X, const void *qw,
-                const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s);
+                const void *scales, const void *zeros, void *Y, const void *residual, void *ws, cudaStream_t s);
 int launch_prepack(qf_ctx *ctx, const void *in, void *out, int64_t n_words, int to_canonical, cudaStream_t s);
 int launch_prepack_tiled(qf_ctx *ctx, const void *in, void *out, int64_t N, int64_t K, int to_canonical,
                          cudaStream_t s);
@@ -172,6 +206,18 @@ int launch_gemv_static(qf_ctx *ctx, const qf_linear_desc *d, const Plan &p, cons
                        const void *scales, const void *zeros, void *Y, cudaStream_t s);
 int gemv_init(qf_ctx *ctx);
 int gemm_init(qf_ctx *ctx);
+// streaming GEMV on QF_LAYOUT_GEMV_SLAB weights (qf_gemv_slab.cu)
+int gemv_slab_init(qf_ctx *ctx);
+int slab_m_pad(int64_t M);
+void slab_geometry(int64_t M, int64_t N, int64_t K, int sm_count, int grid_request, int *grid_out, int *depth_out);
+size_t slab_workspace_bytes(int grid, int64_t M);
+int launch_gemv_slab(qf_ctx *ctx, const qf_linear_desc *d, const Plan &p, const void *X, const void *blob, void *Y,
+                     const void *residual, void *ws, cudaStream_t s);
+int launch_slab_prepack(qf_ctx *ctx, const qf_linear_desc *d, const void *qw, const void *scales, const void *zeros,
+                        void *blob, cudaStream_t s);
+int launch_slab_unpack(qf_ctx *ctx, int64_t N, int64_t K, const void *blob, void *qw, cudaStream_t s);
+int launch_repack_kn(qf_ctx *ctx, const void *w_kn, int packed_along_n, int64_t K, int64_t N, void *out,
+                     cudaStream_t s);
 
 // ---------------------------------------------------------------------------------------------
 // Device helpers: nibble -> f16 / bf16 conversion with zero and scale applied in registers.
@@ -292,6 +338,34 @@ __device__ __forceinline__ void store_out(void *Y, int out_dtype, int64_t idx, f
     } else {
         reinterpret_cast<__nv_bfloat16 *>(Y)[idx] = __float2bfloat16_rn(v);
     }
+}
+
+// Warp-level tensor-core MMA (m16n8k16, fp32 accumulate) and shared-memory loads used by the GEMV kernels.
+template <bool BF16>
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    if (BF16) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+__device__ __forceinline__ uint4 lds128g(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64g(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
 }
 
 // ---------------------------------------------------------------------------------------------

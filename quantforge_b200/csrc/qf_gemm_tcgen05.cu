@@ -28,6 +28,7 @@
 #include <unordered_map>
 
 #include "qf_common.cuh"
+#include "qf_mbar.cuh"
 
 namespace qf {
 
@@ -72,66 +73,48 @@ struct GemmParams {
     int tiled;             // 1: weights stored tile-major (QF_LAYOUT_TILED)
     int cluster_reduce;    // 1: the split_k blocks of a tile form a thread-block cluster and sum their partial
                            //    tiles through distributed shared memory (no global partials, no counters)
+    const void *residual;  // QF_EPI_RESIDUAL_ADD: R[M, N] in out_dtype
+    int epilogue;          // qf_epilogue (plain instantiations only)
 };
+
+__device__ __forceinline__ float gemm_load_out(const void *R, int out_dtype, int64_t idx) {
+    if (out_dtype == QF_F32) return reinterpret_cast<const float *>(R)[idx];
+    if (out_dtype == QF_F16) return __half2float(reinterpret_cast<const __half *>(R)[idx]);
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(R)[idx]);
+}
+__device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.f + expf(-gate)) * up; }
+// Four finished outputs of batch row m, weight rows n..n+3 (n a multiple of 4), with the plain or residual epilogue.
+__device__ __forceinline__ void gemm_store4(const GemmParams &p, int64_t m, int64_t n, float4 a) {
+    const int64_t o = m * p.N + n;
+    if (p.epilogue == QF_EPI_RESIDUAL_ADD) {
+        a.x += gemm_load_out(p.residual, p.out_dtype, o);
+        a.y += gemm_load_out(p.residual, p.out_dtype, o + 1);
+        a.z += gemm_load_out(p.residual, p.out_dtype, o + 2);
+        a.w += gemm_load_out(p.residual, p.out_dtype, o + 3);
+    }
+    store_out(p.Y, p.out_dtype, o, a.x);
+    store_out(p.Y, p.out_dtype, o + 1, a.y);
+    store_out(p.Y, p.out_dtype, o + 2, a.z);
+    store_out(p.Y, p.out_dtype, o + 3, a.w);
+}
+// QF_EPI_SILU_MUL: weight rows n..n+3 (n % 16 < 8) are gate rows, n+8.. the matching up rows; output column
+// (n / 16) * 8 + n % 8 of Y[M, N/2].
+__device__ __forceinline__ void gemm_store4_silu(const GemmParams &p, int64_t m, int64_t n, float4 g, float4 u) {
+    const int64_t o = m * (p.N >> 1) + (n >> 4) * 8 + (n & 7);
+    store_out(p.Y, p.out_dtype, o, silu_mul(g.x, u.x));
+    store_out(p.Y, p.out_dtype, o + 1, silu_mul(g.y, u.y));
+    store_out(p.Y, p.out_dtype, o + 2, silu_mul(g.z, u.z));
+    store_out(p.Y, p.out_dtype, o + 3, silu_mul(g.w, u.w));
+}
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok;
-}
-
-// Bounded wait (about half a second of SM clocks). Returns false on expiry or when another role aborted.
-// A waiting warp backs off with nanosleep so that its polling does not take issue slots from the warps
-// that convert; the sleep is short next to the time a pipeline step takes.
-constexpr long long kWaitCycles = 1000000000LL;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    int it = 0;
-    while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(it < 8 ? 20 : 60);
-        if ((++it & 63) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitCycles) {
-                *abort_flag = 1;
-                return false;
-            }
-        }
-    }
-}
-
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
-}
-// Untiled bulk copy global -> shared (16-byte aligned, size a multiple of 16), completion on an mbarrier.
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -479,9 +462,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                     const int64_t m = m0 + col + j;
                     const float v = __uint_as_float(r[j]);
                     if (p.split_k == 1) {
-                        if (m < p.M) {
-                            if constexpr (EXCH) exch_push(ar, ar_epoch, (size_t)(m * p.N + n), v);
-                            else store_out(p.Y, p.out_dtype, m * p.N + n, v);
+                        if constexpr (EXCH) {
+                            if (m < p.M) exch_push(ar, ar_epoch, (size_t)(m * p.N + n), v);
+                        } else if (p.epilogue == QF_EPI_SILU_MUL) {
+                            // lanes 0-7 and 16-23 of a warp hold gate rows, the lanes 8 above them the up rows
+                            const float up = __shfl_xor_sync(0xffffffffu, v, 8);
+                            if (m < p.M && (row & 8) == 0)
+                                store_out(p.Y, p.out_dtype, m * (p.N >> 1) + (n >> 4) * 8 + (n & 7), silu_mul(v, up));
+                        } else if (m < p.M) {
+                            const float res =
+                                p.epilogue == QF_EPI_RESIDUAL_ADD ? gemm_load_out(p.residual, p.out_dtype, m * p.N + n) : 0.f;
+                            store_out(p.Y, p.out_dtype, m * p.N + n, v + res);
                         }
                     } else if (CLUSTER_OK && p.cluster_reduce) {
                         // partial tile [batch row][weight row] fp32 in the (now idle) pipeline stages
@@ -518,7 +509,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
             for (int u = split * per + tid; u < u_end; u += GEMM_THREADS) {
                 const int nl = (u & 31) * 4;
                 const int64_t m = m0 + (u >> 5);
-                if (m < p.M) {
+                const bool silu = p.epilogue == QF_EPI_SILU_MUL;
+                if (m < p.M && !(silu && (nl & 8))) {
                     const uint32_t a = smem_base + (uint32_t)((u >> 5) * 128 + nl) * 4u;
                     float4 v[8];
 #pragma unroll
@@ -532,11 +524,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                         acc.z += v[sp].z;
                         acc.w += v[sp].w;
                     }
-                    const int64_t o = m * p.N + n0 + nl;
-                    store_out(p.Y, p.out_dtype, o, acc.x);
-                    store_out(p.Y, p.out_dtype, o + 1, acc.y);
-                    store_out(p.Y, p.out_dtype, o + 2, acc.z);
-                    store_out(p.Y, p.out_dtype, o + 3, acc.w);
+                    if (silu) {
+                        // the matching up rows sit 8 rows further on
+#pragma unroll
+                        for (int sp = 0; sp < 8; ++sp)
+                            v[sp] = sp < p.split_k ? ld_dsmem_f4(dsmem_addr(a + 32u, (uint32_t)sp))
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+                        float4 up = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int sp = 0; sp < 8; ++sp) {
+                            up.x += v[sp].x;
+                            up.y += v[sp].y;
+                            up.z += v[sp].z;
+                            up.w += v[sp].w;
+                        }
+                        gemm_store4_silu(p, m, n0 + nl, acc, up);
+                    } else {
+                        gemm_store4(p, m, n0 + nl, acc);
+                    }
                 }
             }
         }
@@ -576,33 +581,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                 for (int u = tid; u < 32 * BN; u += GEMM_THREADS) {
                     const int nl = (u & 31) * 4;
                     const int64_t m = m0 + (u >> 5);
-                    if (m < p.M) {
-                        const float *base = p.partial + (size_t)m * p.N + n0 + nl;
-                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                        for (int sp0 = 0; sp0 < p.split_k; sp0 += 4) {
-                            float4 v[4];
+                    const bool silu = !EXCH && p.epilogue == QF_EPI_SILU_MUL;
+                    if (m < p.M && !(silu && (nl & 8))) {
+                        // sum over the splits of 4 consecutive output columns starting `off` columns into the row
+                        auto sum4 = [&](int off) {
+                            const float *base = p.partial + (size_t)m * p.N + n0 + nl + off;
+                            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                            for (int sp0 = 0; sp0 < p.split_k; sp0 += 4) {
+                                float4 v[4];
 #pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                v[j] = (sp0 + j < p.split_k)
-                                           ? __ldcg(reinterpret_cast<const float4 *>(base + (size_t)(sp0 + j) * split_stride))
-                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+                                for (int j = 0; j < 4; ++j)
+                                    v[j] = (sp0 + j < p.split_k)
+                                               ? __ldcg(reinterpret_cast<const float4 *>(base + (size_t)(sp0 + j) * split_stride))
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                acc.x += v[j].x;
-                                acc.y += v[j].y;
-                                acc.z += v[j].z;
-                                acc.w += v[j].w;
+                                for (int j = 0; j < 4; ++j) {
+                                    acc.x += v[j].x;
+                                    acc.y += v[j].y;
+                                    acc.z += v[j].z;
+                                    acc.w += v[j].w;
+                                }
                             }
-                        }
+                            return acc;
+                        };
+                        const float4 acc = sum4(0);
                         const int64_t o = m * p.N + n0 + nl;
                         if constexpr (EXCH) {
                             exch_push2(ar, ar_epoch, (size_t)o, acc.x, acc.y);
                             exch_push2(ar, ar_epoch, (size_t)o + 2, acc.z, acc.w);
+                        } else if (silu) {
+                            gemm_store4_silu(p, m, n0 + nl, acc, sum4(8));
                         } else {
-                            store_out(p.Y, p.out_dtype, o, acc.x);
-                            store_out(p.Y, p.out_dtype, o + 1, acc.y);
-                            store_out(p.Y, p.out_dtype, o + 2, acc.z);
-                            store_out(p.Y, p.out_dtype, o + 3, acc.w);
+                            gemm_store4(p, m, n0 + nl, acc);
                         }
                     }
                 }
@@ -794,9 +804,11 @@ static int gemm_launch_dt(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan
 int gemm_block_k(int bn) { return bn <= 128 ? 128 : 64; }
 
 static int launch_gemm_impl(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
-                            const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s,
-                            const ArParams *ar) {
+                            const void *scales, const void *zeros, void *Y, const void *residual, void *ws,
+                            cudaStream_t s, const ArParams *ar) {
     GemmParams p;
+    p.residual = residual;
+    p.epilogue = ar ? QF_EPI_NONE : d->epilogue;
     p.scales = (const uint16_t *)scales;
     p.zeros = zeros;
     p.Y = Y;
@@ -819,13 +831,13 @@ static int launch_gemm_impl(qf_ctx *ctx, const qf_linear_desc *d, const Plan &pl
 }
 
 int launch_gemm(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
-                const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s) {
-    return launch_gemm_impl(ctx, d, plan, X, qw, scales, zeros, Y, ws, s, nullptr);
+                const void *scales, const void *zeros, void *Y, const void *residual, void *ws, cudaStream_t s) {
+    return launch_gemm_impl(ctx, d, plan, X, qw, scales, zeros, Y, residual, ws, s, nullptr);
 }
 
 int launch_gemm_ar(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *qw,
                    const void *scales, const void *zeros, void *Y, void *ws, cudaStream_t s, const ArParams &ar) {
-    return launch_gemm_impl(ctx, d, plan, X, qw, scales, zeros, Y, ws, s, &ar);
+    return launch_gemm_impl(ctx, d, plan, X, qw, scales, zeros, Y, nullptr, ws, s, &ar);
 }
 
 }  // namespace qf

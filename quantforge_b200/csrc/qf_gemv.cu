@@ -57,22 +57,6 @@ static inline size_t gemv_smem_bytes(int chunks_per_split, int m_pad) {
            (size_t)chunks_per_split * 4 * m_pad * 4 * 16;
 }
 
-template <bool BF16>
-__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                          uint32_t b0, uint32_t b1) {
-    if (BF16) {
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-    } else {
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-    }
-}
-
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -81,17 +65,6 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
-__device__ __forceinline__ uint4 lds128g(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint2 lds64g(uint32_t addr) {
-    uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-    return v;
-}
-
 // Converter constants from a table entry (x = magic+zero duplicated, y = scale duplicated).
 template <bool BF16>
 __device__ __forceinline__ ZeroScale<BF16> consts_from(const uint2 e) {
@@ -527,7 +500,10 @@ int launch_gemv_static(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, c
         return fail(ctx, QF_ERR_WORKSPACE,
                     "this linear needs " + std::to_string(need) + " bytes of split-K scratch but the static array holds " +
                         std::to_string((size_t)QF_STATIC_SCRATCH_BYTES) +
-                        "; pass split_k = 1 or use qf_w4a16_linear with a caller workspace");
+                        (d->K <= 128 * GEMV_MAX_CHUNKS_PER_SPLIT
+                             ? "; request split_k = 1 (no scratch at all for this K) or use qf_w4a16_linear with a caller "
+                               "workspace"
+                             : "; use qf_w4a16_linear with a caller workspace (K this long is always split)"));
     void *scratch = nullptr;
     int st = static_scratch_for_current_device(ctx, &scratch);
     if (st != QF_OK) return st;

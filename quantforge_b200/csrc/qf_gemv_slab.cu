@@ -1,0 +1,594 @@
+// K2s: streaming W4A16 GEMV / skinny GEMM (M <= 32) on QF_LAYOUT_GEMV_SLAB weights, HBM-bound.
+//
+// Y[M,N] = X[M,K] . W^T with W dequantised in registers (same converter as every other kernel here) and never
+// written to memory.
+//
+// Work split. The weight matrix is cut into units of 64 rows x 128 codes (one QF_SLAB_UNIT_BYTES record of the
+// blob: codes, scales and zeros of the unit, in consumption order). Units are numbered row block major, K chunk
+// minor, and thread block i of G owns the CONTIGUOUS range [i*U/G, (i+1)*U/G): every block streams the same number
+// of bytes (+-1 unit) from one contiguous range of HBM, whatever N and K are. G is a small multiple of the SM
+// count, so the whole launch is resident at once.
+//
+// Inside a block (160 threads):
+//   warp 4      producer: one cp.async.bulk per unit into a ring of shared-memory stages (full / empty mbarriers),
+//               plus one 256-byte bulk copy per batch row for the unit's slice of X. All weight copies of the
+//               first pass over the ring are issued BEFORE the programmatic-dependent-launch wait (weights do not
+//               depend on the previous kernel of the stream), the activation copies after it.
+//   warps 0-3   consumers: warp w owns rows 16w..16w+15 of the unit. Per unit and lane: 2 x 16 B of codes and two
+//               constants words from shared memory -> lop3 / packed 16-bit arithmetic -> A fragments of
+//               m16n8k16 tensor-core MMAs; B fragments are 16-byte reads of the natural-order activation slice
+//               (the blob's nibble order makes adjacent codes adjacent halves of a register). fp32 accumulators.
+//
+// Row blocks whose K range is shared by several thread blocks (the ranges do not end on row-block boundaries):
+// the thread block that holds the END of the row block's K range is its owner. It meets that segment first (its
+// range starts in the middle of the row block), keeps the partial sums in registers and finishes the row block
+// at the very end of its life; every other contributor leaves its partial sums in the workspace as 8-byte
+// (value, token) words - no fence, no atomic, no wait on the contributor's side. The owner reads them (polling
+// the tokens, bounded), sums in thread-block order (deterministic), writes Y and clears the tokens, which is what
+// leaves the workspace ready for the next launch. An owner only ever waits for thread blocks with a LOWER index,
+// which were dispatched before it.
+#include <algorithm>
+#include <cstdlib>
+
+#include "qf_common.cuh"
+#include "qf_mbar.cuh"
+
+namespace qf {
+
+constexpr int SLAB_THREADS = 160;
+constexpr int SLAB_TILE_BYTES = 1088;           // 2 x 512 B of codes + 64 B of constants
+constexpr int SLAB_UNIT_BYTES = QF_SLAB_UNIT_BYTES;
+constexpr int SLAB_X_PITCH = 320;               // bytes between batch rows of a stage's activation slice (256 + 64
+                                                // of skew: rows g and g+1 land in different shared-memory banks)
+constexpr int SLAB_MAX_DEPTH = 16;
+static_assert(SLAB_UNIT_BYTES == 4 * SLAB_TILE_BYTES, "unit = 4 tiles");
+
+struct SlabParams {
+    const uint8_t *blob;
+    const uint16_t *X;
+    void *Y;
+    const void *residual;
+    unsigned long long *pairs;  // workspace: [G][4 warps][MT][32 lanes][4] (value | token << 32), zero between launches
+    int *status;                // host-mapped status word of the context
+    int64_t M, N, K;
+    long long units;            // (N / 64) * (K / 128)
+    int chunks;                 // K / 128
+    int depth;                  // stages of the ring
+    int m_pad;                  // batch rows a stage has room for: 1, 2, 4, 8, 16 or 32
+    int out_dtype;
+    int epilogue;
+};
+
+__device__ __forceinline__ uint32_t lds32g(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+// Two (value, token) words with one 16-byte access; each 8-byte word is written and read whole.
+__device__ __forceinline__ void st_pairs2(unsigned long long *ptr, unsigned long long a, unsigned long long b) {
+    asm volatile("st.relaxed.gpu.global.v2.b64 [%0], {%1, %2};" ::"l"(ptr), "l"(a), "l"(b) : "memory");
+}
+__device__ __forceinline__ void ld_pairs2(const unsigned long long *ptr, unsigned long long &a, unsigned long long &b) {
+    asm volatile("ld.relaxed.gpu.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(ptr) : "memory");
+}
+__device__ __forceinline__ unsigned long long pair_of(float v) {
+    return (unsigned long long)__float_as_uint(v) | (1ull << 32);
+}
+
+__device__ __forceinline__ float load_out(const void *R, int out_dtype, int64_t idx) {
+    if (out_dtype == QF_F32) return reinterpret_cast<const float *>(R)[idx];
+    if (out_dtype == QF_F16) return __half2float(reinterpret_cast<const __half *>(R)[idx]);
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(R)[idx]);
+}
+
+// Thread block that owns unit u under the partition [i*U/G, (i+1)*U/G): the largest i with i*U/G <= u.
+__device__ __forceinline__ long long slab_cta_of(long long u, long long U, long long G) {
+    return ((u + 1) * G - 1) / U;
+}
+
+template <bool BF16>
+__device__ __forceinline__ ZeroScale<BF16> slab_consts(uint32_t word) {
+    ZeroScale<BF16> zs;
+    zs.zsub = prmt(word, word, 0x1010u);
+    zs.s2 = prmt(word, word, 0x3232u);
+    // f16 only: -(64 + z) = (1024 + z) * (-1) + 960, exact in f16
+    zs.zfma = BF16 ? 0u : fma_f16x2(zs.zsub, 0xbc00bc00u, 0x63806380u);
+    return zs;
+}
+
+// Writes the finished 16 x M outputs a warp holds for weight rows n0 + {g, g+8} (lane = 4g + t owns batch rows
+// nt*8 + 2t + {0, 1}).
+template <int MT>
+__device__ __forceinline__ void slab_store(const SlabParams &p, int64_t n0, int g, int t, const float (&v)[MT][4]) {
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int64_t m = nt * 8 + 2 * t + e;
+            if (m >= p.M) continue;
+            if (p.epilogue == QF_EPI_SILU_MUL) {
+                // rows g of the tile are gate rows, rows g+8 the matching up rows
+                const float gate = v[nt][e], up = v[nt][2 + e];
+                store_out(p.Y, p.out_dtype, m * (p.N >> 1) + (n0 >> 1) + g, gate / (1.f + expf(-gate)) * up);
+            } else {
+                const int64_t ia = m * p.N + n0 + g, ib = ia + 8;
+                float a = v[nt][e], b = v[nt][2 + e];
+                if (p.epilogue == QF_EPI_RESIDUAL_ADD) {
+                    a += load_out(p.residual, p.out_dtype, ia);
+                    b += load_out(p.residual, p.out_dtype, ib);
+                }
+                store_out(p.Y, p.out_dtype, ia, a);
+                store_out(p.Y, p.out_dtype, ib, b);
+            }
+        }
+}
+
+template <bool BF16, int MT>
+__global__ void __launch_bounds__(SLAB_THREADS) gemv_slab_kernel(const SlabParams p) {
+    extern __shared__ __align__(128) uint8_t slab_smem[];
+    __shared__ int s_abort;
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const uint32_t stage_bytes = (uint32_t)SLAB_UNIT_BYTES + (uint32_t)p.m_pad * SLAB_X_PITCH;
+    const uint32_t ring = (smem_u32(slab_smem) + 127u) & ~127u;
+    const uint32_t bar_base = ring + (uint32_t)p.depth * stage_bytes;
+    auto stage = [&](int s) { return ring + (uint32_t)s * stage_bytes; };
+    auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(p.depth + s); };
+
+    const long long G = gridDim.x;
+    const long long cta = blockIdx.x;
+    const long long u0 = cta * p.units / G;
+    const int n_units = (int)((cta + 1) * p.units / G - u0);
+    volatile int *abort_flag = &s_abort;
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < p.depth; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    griddep_launch_dependents();  // the next kernel of the stream may start its own weight prefetch
+
+    if (warp == 4) {
+        // ------------------------------ producer ------------------------------
+        const int M = (int)p.M;
+        const uint32_t tx = (uint32_t)SLAB_UNIT_BYTES + (uint32_t)M * 256u;
+        const uint8_t *src = p.blob + (size_t)u0 * SLAB_UNIT_BYTES;
+        const int npre = min(p.depth, n_units);
+        int issued = 0;
+        if (lane == 0)
+            for (int it = 0; it < npre; ++it) {
+                mbar_arrive_expect_tx(full_bar(it), tx);
+                bulk_load(stage(it), src + (size_t)it * SLAB_UNIT_BYTES, SLAB_UNIT_BYTES, full_bar(it));
+            }
+        __syncwarp();
+        griddep_wait();  // the activations are the previous kernel's output
+        int c = (int)(u0 % p.chunks);
+        for (int it = 0; it < npre; ++it) {
+            if (lane < M)
+                bulk_load(stage(it) + SLAB_UNIT_BYTES + (uint32_t)lane * SLAB_X_PITCH,
+                          p.X + (size_t)lane * p.K + (size_t)c * 128, 256u, full_bar(it));
+            if (++c == p.chunks) c = 0;
+        }
+        issued = npre;
+        for (int it = npre; it < n_units; ++it) {
+            const int s = it % p.depth;
+            const uint32_t ph = (uint32_t)((it / p.depth) - 1) & 1u;
+            const bool ok = mbar_wait(empty_bar(s), ph, abort_flag);
+            if (!__all_sync(0xffffffffu, ok)) break;
+            if (lane == 0) {
+                mbar_arrive_expect_tx(full_bar(s), tx);
+                bulk_load(stage(s), src + (size_t)it * SLAB_UNIT_BYTES, SLAB_UNIT_BYTES, full_bar(s));
+            }
+            __syncwarp();
+            if (lane < M)
+                bulk_load(stage(s) + SLAB_UNIT_BYTES + (uint32_t)lane * SLAB_X_PITCH,
+                          p.X + (size_t)lane * p.K + (size_t)c * 128, 256u, full_bar(s));
+            if (++c == p.chunks) c = 0;
+            issued = it + 1;
+        }
+        if (s_abort) {
+            // drain this block's own copies before its shared memory goes away (the consumers stopped waiting)
+            int dummy = 0;
+            volatile int *no_abort = &dummy;
+            for (int it = max(0, issued - p.depth); it < issued; ++it)
+                mbar_wait(full_bar(it % p.depth), (uint32_t)(it / p.depth) & 1u, no_abort);
+            if (lane == 0) atomicExch(p.status, QF_ERR_TIMEOUT);
+        }
+        return;
+    }
+
+    // ------------------------------ consumers ------------------------------
+    griddep_wait();  // nothing to compute before the activations exist; the bounded waits below start after it
+    const int g = lane >> 2;
+    const int t = lane & 3;
+    float acc[MT][2][4];
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[nt][h][e] = 0.f;
+    float held[MT][4];
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) held[nt][e] = 0.f;
+    bool have_held = false;
+    long long held_b = 0;
+    long long b = u0 / p.chunks;
+    int c = (int)(u0 % p.chunks);
+    int c_lo = c;
+    unsigned long long *my_pairs = p.pairs + (((size_t)cta * 4 + warp) * MT) * 128 + lane * 4;
+    bool aborted = false;
+
+#pragma unroll 1
+    for (int it = 0; it < n_units; ++it) {
+        const int s = it % p.depth;
+        const bool ok = mbar_wait(full_bar(s), (uint32_t)(it / p.depth) & 1u, abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) {
+            aborted = true;
+            break;
+        }
+        const uint32_t tile = stage(s) + (uint32_t)warp * SLAB_TILE_BYTES;
+        const uint4 va = lds128g(tile + (uint32_t)lane * 16u);
+        const uint4 vb = lds128g(tile + 512u + (uint32_t)lane * 16u);
+        const ZeroScale<BF16> za = slab_consts<BF16>(lds32g(tile + 1024u + (uint32_t)g * 4u));
+        const ZeroScale<BF16> zb = slab_consts<BF16>(lds32g(tile + 1024u + (uint32_t)(g + 8) * 4u));
+        const uint32_t xbase = stage(s) + SLAB_UNIT_BYTES + (uint32_t)t * 16u;
+        const uint32_t wa[4] = {va.x, va.y, va.z, va.w};
+        const uint32_t wb[4] = {vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t pa[4], pb[4];
+            dequant8<BF16>(wa[j], za, pa);
+            dequant8<BF16>(wb[j], zb, pb);
+#pragma unroll
+            for (int nt = 0; nt < MT; ++nt) {
+                // batch rows beyond m_pad are never stored: wrap into the rows the stage holds
+                const uint32_t row = (uint32_t)((nt * 8 + g) & (p.m_pad - 1));
+                const uint4 xb = lds128g(xbase + row * SLAB_X_PITCH + (uint32_t)j * 64u);
+                mma_16816<BF16>(acc[nt][0], pa[0], pb[0], pa[1], pb[1], xb.x, xb.y);
+                mma_16816<BF16>(acc[nt][1], pa[2], pb[2], pa[3], pb[3], xb.z, xb.w);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(s));
+        ++c;
+        if (c == p.chunks || it == n_units - 1) {
+            // end of this block's share of row block b
+            float v[MT][4];
+#pragma unroll
+            for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    v[nt][e] = acc[nt][0][e] + acc[nt][1][e];
+                    acc[nt][0][e] = 0.f;
+                    acc[nt][1][e] = 0.f;
+                }
+            if (c_lo == 0 && c == p.chunks) {
+                slab_store<MT>(p, b * 64 + warp * 16, g, t, v);
+            } else if (c == p.chunks) {
+                // this block owns row block b (it holds the end of its K range): finished at the very end
+#pragma unroll
+                for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) held[nt][e] = v[nt][e];
+                have_held = true;
+                held_b = b;
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < MT; ++nt) {
+                    st_pairs2(my_pairs + nt * 128, pair_of(v[nt][0]), pair_of(v[nt][1]));
+                    st_pairs2(my_pairs + nt * 128 + 2, pair_of(v[nt][2]), pair_of(v[nt][3]));
+                }
+            }
+            if (c == p.chunks) {
+                c = 0;
+                ++b;
+            }
+            c_lo = c;
+        }
+    }
+
+    if (aborted && lane == 0) atomicExch(p.status, QF_ERR_TIMEOUT);
+    if (have_held && !aborted) {
+        // contributors of row block held_b: the thread blocks from the one that holds its first unit up to cta - 1,
+        // added in that order onto this block's own partial sums
+        const long long first = slab_cta_of(held_b * p.chunks, p.units, G);
+        constexpr int BATCH = MT == 1 ? 4 : MT == 2 ? 2 : 1;  // contributors whose words are in flight together
+        const long long t0 = clock64();
+        bool failed = false;
+#pragma unroll 1
+        for (long long j0 = first; j0 < cta; j0 += BATCH) {
+            unsigned long long w[BATCH][MT][4];
+            bool need[BATCH];
+#pragma unroll
+            for (int q = 0; q < BATCH; ++q) need[q] = j0 + q < cta;
+            while (true) {
+                bool miss = false;
+#pragma unroll
+                for (int q = 0; q < BATCH; ++q)
+                    if (need[q]) {
+                        const unsigned long long *src = p.pairs + (((size_t)(j0 + q) * 4 + warp) * MT) * 128 + lane * 4;
+#pragma unroll
+                        for (int nt = 0; nt < MT; ++nt) {
+                            ld_pairs2(src + nt * 128, w[q][nt][0], w[q][nt][1]);
+                            ld_pairs2(src + nt * 128 + 2, w[q][nt][2], w[q][nt][3]);
+                        }
+                    }
+#pragma unroll
+                for (int q = 0; q < BATCH; ++q)
+                    if (need[q]) {
+                        bool all = true;
+#pragma unroll
+                        for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) all = all && (w[q][nt][e] >> 32) == 1ull;
+                        if (all) need[q] = false;  // arrived: its words stay in w[q]
+                        else miss = true;
+                    }
+                if (!__any_sync(0xffffffffu, miss)) break;
+                __nanosleep(100);
+                // warp-uniform decision: the votes above and below are executed by all 32 lanes
+                if (__any_sync(0xffffffffu, clock64() - t0 > kWaitCycles || *abort_flag != 0)) {
+                    failed = true;
+                    break;
+                }
+            }
+            if (failed) break;
+#pragma unroll
+            for (int q = 0; q < BATCH; ++q)
+                if (j0 + q < cta) {
+                    unsigned long long *src = p.pairs + (((size_t)(j0 + q) * 4 + warp) * MT) * 128 + lane * 4;
+#pragma unroll
+                    for (int nt = 0; nt < MT; ++nt) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) held[nt][e] += __uint_as_float((unsigned)w[q][nt][e]);
+                        st_pairs2(src + nt * 128, 0ull, 0ull);  // ready for the next launch
+                        st_pairs2(src + nt * 128 + 2, 0ull, 0ull);
+                    }
+                }
+        }
+        if (!failed) {
+            slab_store<MT>(p, held_b * 64 + warp * 16, g, t, held);
+        } else if (lane == 0) {
+            *abort_flag = 1;
+            atomicExch(p.status, QF_ERR_TIMEOUT);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// prepack: canonical qweight + scales + zeros -> blob, and the inverse for the codes
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t slab_interleave_word(uint32_t w) {
+    uint32_t r = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        r |= ((w >> (8 * i)) & 0xFu) << (4 * i);            // even codes -> nibbles 0..3
+        r |= ((w >> (8 * i + 4)) & 0xFu) << (4 * (i + 4));  // odd codes  -> nibbles 4..7
+    }
+    return r;
+}
+__device__ __forceinline__ uint32_t slab_deinterleave_word(uint32_t w) {
+    uint32_t r = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        r |= ((w >> (4 * i)) & 0xFu) << (8 * i);
+        r |= ((w >> (4 * (i + 4))) & 0xFu) << (8 * i + 4);
+    }
+    return r;
+}
+
+// One thread per 32-bit word of the blob's code area (272 words per tile, the last 16 of them constants).
+template <bool BF16, int ZMODE>
+__global__ void __launch_bounds__(256) slab_prepack_kernel(const uint32_t *__restrict__ qw,
+                                                           const uint16_t *__restrict__ scales,
+                                                           const void *__restrict__ zeros, int zero_const,
+                                                           uint32_t *__restrict__ blob, int64_t N, int64_t K,
+                                                           int group) {
+    const int64_t chunks = K >> 7;
+    const int64_t tiles = (N >> 4) * chunks;
+    const int64_t total = tiles * 272;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t tile = i / 272;
+        const int w = (int)(i - tile * 272);
+        const int64_t unit = tile >> 2;
+        const int warp = (int)(tile & 3);
+        const int64_t b = unit / chunks;
+        const int64_t c = unit - b * chunks;
+        const int64_t row0 = b * 64 + warp * 16;
+        if (w < 256) {
+            const int half = w >> 7;          // rows g or g + 8
+            const int lane = (w >> 2) & 31;
+            const int j = w & 3;
+            const int64_t row = row0 + (lane >> 2) + 8 * half;
+            const int64_t word = c * 16 + 4 * j + (lane & 3);
+            blob[i] = slab_interleave_word(qw[row * (K >> 3) + word]);
+        } else {
+            const int64_t n = row0 + (w - 256);
+            const int64_t gi = (c * 128) / group;
+            const int z = load_zero<ZMODE>(zeros, zero_const, gi, n, N);
+            const uint32_t zsub = BF16 ? int_to_bf16_bits(128 + z) : int_to_f16_bits(1024 + z);
+            blob[i] = (zsub & 0xffffu) | ((uint32_t)scales[gi * N + n] << 16);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) slab_unpack_kernel(const uint32_t *__restrict__ blob, uint32_t *__restrict__ qw,
+                                                          int64_t N, int64_t K) {
+    const int64_t chunks = K >> 7;
+    const int64_t tiles = (N >> 4) * chunks;
+    const int64_t total = tiles * 256;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t tile = i >> 8;
+        const int w = (int)(i & 255);
+        const int64_t unit = tile >> 2;
+        const int warp = (int)(tile & 3);
+        const int64_t b = unit / chunks;
+        const int64_t c = unit - b * chunks;
+        const int half = w >> 7;
+        const int lane = (w >> 2) & 31;
+        const int j = w & 3;
+        const int64_t row = b * 64 + warp * 16 + (lane >> 2) + 8 * half;
+        const int64_t word = c * 16 + 4 * j + (lane & 3);
+        qw[row * (K >> 3) + word] = slab_deinterleave_word(blob[tile * 272 + w]);
+    }
+}
+
+template <bool BF16>
+static void slab_prepack_dispatch(int zmode, unsigned blocks, cudaStream_t s, const uint32_t *qw, const uint16_t *sc,
+                                  const void *z, int zc, uint32_t *blob, int64_t N, int64_t K, int group) {
+    if (zmode == QF_ZERO_CONST)
+        slab_prepack_kernel<BF16, QF_ZERO_CONST><<<blocks, 256, 0, s>>>(qw, sc, z, zc, blob, N, K, group);
+    else if (zmode == QF_ZERO_U4)
+        slab_prepack_kernel<BF16, QF_ZERO_U4><<<blocks, 256, 0, s>>>(qw, sc, z, zc, blob, N, K, group);
+    else
+        slab_prepack_kernel<BF16, QF_ZERO_I8><<<blocks, 256, 0, s>>>(qw, sc, z, zc, blob, N, K, group);
+}
+
+int launch_slab_prepack(qf_ctx *ctx, const qf_linear_desc *d, const void *qw, const void *scales, const void *zeros,
+                        void *blob, cudaStream_t s) {
+    const int64_t total = (d->N / 16) * (d->K / 128) * 272;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
+    if (d->act_dtype == QF_BF16)
+        slab_prepack_dispatch<true>(d->zero_mode, (unsigned)blocks, s, (const uint32_t *)qw, (const uint16_t *)scales,
+                                    zeros, d->zero_const, (uint32_t *)blob, d->N, d->K, d->group_size);
+    else
+        slab_prepack_dispatch<false>(d->zero_mode, (unsigned)blocks, s, (const uint32_t *)qw, (const uint16_t *)scales,
+                                     zeros, d->zero_const, (uint32_t *)blob, d->N, d->K, d->group_size);
+    g_launch_count.fetch_add(1);
+    QF_CUDA_TRY(ctx, cudaGetLastError());
+    return QF_OK;
+}
+
+int launch_slab_unpack(qf_ctx *ctx, int64_t N, int64_t K, const void *blob, void *qw, cudaStream_t s) {
+    const int64_t total = (N / 16) * (K / 128) * 256;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
+    slab_unpack_kernel<<<(unsigned)blocks, 256, 0, s>>>((const uint32_t *)blob, (uint32_t *)qw, N, K);
+    g_launch_count.fetch_add(1);
+    QF_CUDA_TRY(ctx, cudaGetLastError());
+    return QF_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+static size_t slab_smem_bytes(int depth, int m_pad) {
+    return (size_t)depth * (SLAB_UNIT_BYTES + m_pad * SLAB_X_PITCH) + 2 * (size_t)depth * 8 + 128 /*alignment*/;
+}
+
+int slab_m_pad(int64_t M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : M <= 16 ? 16 : 32; }
+
+// Thread blocks per SM and ring depth for a launch. Small matrices: more, shorter thread blocks (every block's
+// weights are in flight at once and there is room for the next kernel's blocks beside them); large ones: deep
+// rings. QF_SLAB_CTAS / QF_SLAB_DEPTH in the environment override the heuristic (tuning).
+void slab_geometry(int64_t M, int64_t N, int64_t K, int sm_count, int grid_request, int *grid_out, int *depth_out) {
+    // read on every call (a tuning run changes them between launches); two getenv calls cost nothing next to a launch
+    const char *e_ctas = std::getenv("QF_SLAB_CTAS");
+    const char *e_depth = std::getenv("QF_SLAB_DEPTH");
+    const int env_ctas = e_ctas ? std::atoi(e_ctas) : 0;
+    const int env_depth = e_depth ? std::atoi(e_depth) : 0;
+    const long long units = (N / 64) * (K / 128);
+    const int m_pad = slab_m_pad(M);
+    const size_t stage = SLAB_UNIT_BYTES + (size_t)m_pad * SLAB_X_PITCH;
+    int ctas = 1;
+    for (int cand = 4; cand >= 1; --cand) {
+        const long long per = units / ((long long)sm_count * cand);
+        const long long fit = (long long)((200u << 10) / cand / stage);
+        if ((per >= 4 && fit >= 6) || cand == 1) {
+            ctas = cand;
+            break;
+        }
+    }
+    if (env_ctas > 0) ctas = env_ctas;
+    long long grid = (long long)sm_count * ctas;
+    if (grid_request > 0) {
+        // an explicit number of thread blocks (tests, tuning): any value works, an owner only waits for thread
+        // blocks dispatched before it
+        grid = grid_request;
+        ctas = (int)std::min<long long>(4, std::max<long long>(1, (grid + sm_count - 1) / sm_count));
+    }
+    if (grid > units) grid = units;
+    long long depth = (long long)((200u << 10) / ctas / stage);
+    const long long per_max = (units + grid - 1) / grid;
+    if (depth > per_max) depth = per_max;
+    if (depth > SLAB_MAX_DEPTH) depth = SLAB_MAX_DEPTH;
+    if (env_depth > 0) depth = env_depth;
+    if (depth < 1) depth = 1;
+    while (depth > 1 && slab_smem_bytes((int)depth, m_pad) > (size_t)(220u << 10)) --depth;
+    *grid_out = (int)grid;
+    *depth_out = (int)depth;
+}
+
+size_t slab_workspace_bytes(int grid, int64_t M) {
+    const int mt = (slab_m_pad(M) + 7) / 8;
+    return (size_t)grid * 4 * mt * 128 * sizeof(unsigned long long);
+}
+
+template <bool BF16, int MT>
+static cudaError_t slab_set_attr() {
+    return cudaFuncSetAttribute(gemv_slab_kernel<BF16, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)(220u << 10));
+}
+
+int gemv_slab_init(qf_ctx *ctx) {
+    QF_CUDA_TRY(ctx, (slab_set_attr<false, 1>()));
+    QF_CUDA_TRY(ctx, (slab_set_attr<false, 2>()));
+    QF_CUDA_TRY(ctx, (slab_set_attr<false, 4>()));
+    QF_CUDA_TRY(ctx, (slab_set_attr<true, 1>()));
+    QF_CUDA_TRY(ctx, (slab_set_attr<true, 2>()));
+    QF_CUDA_TRY(ctx, (slab_set_attr<true, 4>()));
+    return QF_OK;
+}
+
+int launch_gemv_slab(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *blob, void *Y,
+                     const void *residual, void *ws, cudaStream_t s) {
+    SlabParams p;
+    p.blob = (const uint8_t *)blob;
+    p.X = (const uint16_t *)X;
+    p.Y = Y;
+    p.residual = residual;
+    p.pairs = (unsigned long long *)ws;
+    p.status = ctx->dev_status;
+    p.M = d->M;
+    p.N = d->N;
+    p.K = d->K;
+    p.chunks = (int)(d->K / 128);
+    p.units = (long long)(d->N / 64) * p.chunks;
+    p.depth = plan.chunks_per_split;
+    p.m_pad = slab_m_pad(d->M);
+    p.out_dtype = d->out_dtype;
+    p.epilogue = d->epilogue;
+    const dim3 grid((unsigned)plan.split_k), blk(SLAB_THREADS);
+    const size_t smem = slab_smem_bytes(p.depth, p.m_pad);
+    const bool pdl = pdl_enabled();
+    const int mt = (p.m_pad + 7) / 8;
+    cudaError_t le;
+    if (d->act_dtype == QF_BF16) {
+        le = mt == 1   ? launch_kernel(gemv_slab_kernel<true, 1>, grid, blk, smem, s, pdl, p)
+             : mt == 2 ? launch_kernel(gemv_slab_kernel<true, 2>, grid, blk, smem, s, pdl, p)
+                       : launch_kernel(gemv_slab_kernel<true, 4>, grid, blk, smem, s, pdl, p);
+    } else {
+        le = mt == 1   ? launch_kernel(gemv_slab_kernel<false, 1>, grid, blk, smem, s, pdl, p)
+             : mt == 2 ? launch_kernel(gemv_slab_kernel<false, 2>, grid, blk, smem, s, pdl, p)
+                       : launch_kernel(gemv_slab_kernel<false, 4>, grid, blk, smem, s, pdl, p);
+    }
+    g_launch_count.fetch_add(1);
+    QF_CUDA_TRY(ctx, le);
+    QF_CUDA_TRY(ctx, cudaGetLastError());
+    return QF_OK;
+}
+
+}  // namespace qf

@@ -141,6 +141,44 @@ int launch_prepack_tiled(qf_ctx *ctx, const void *in, void *out, int64_t N, int6
     return QF_OK;
 }
 
+// W[K, N] (one code per byte, or two per byte along N) -> canonical qweight [N, K/8] words. One thread per output
+// word; consecutive threads take consecutive n, so the reads are coalesced (the 4-byte writes are not: one-time op).
+__global__ void __launch_bounds__(256) repack_kn_kernel(const uint8_t *__restrict__ w_kn, int packed_along_n,
+                                                        int64_t K, int64_t N, uint32_t *__restrict__ out) {
+    const int64_t words_per_row = K >> 3;
+    const int64_t total = N * words_per_row;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t n = i % N;
+        const int64_t j = i / N;
+        uint32_t word = 0;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const int64_t k = 8 * j + c;
+            uint32_t code;
+            if (packed_along_n) {
+                const uint32_t b = w_kn[k * (N >> 1) + (n >> 1)];
+                code = (n & 1) ? (b >> 4) & 0xFu : b & 0xFu;
+            } else {
+                code = w_kn[k * N + n] & 0xFu;
+            }
+            word |= code << (4 * c);
+        }
+        out[n * words_per_row + j] = word;
+    }
+}
+
+int launch_repack_kn(qf_ctx *ctx, const void *w_kn, int packed_along_n, int64_t K, int64_t N, void *out,
+                     cudaStream_t s) {
+    const int64_t total = N * (K / 8);
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
+    repack_kn_kernel<<<(unsigned)blocks, 256, 0, s>>>((const uint8_t *)w_kn, packed_along_n, K, N, (uint32_t *)out);
+    g_launch_count.fetch_add(1);
+    QF_CUDA_TRY(ctx, cudaGetLastError());
+    return QF_OK;
+}
+
 // One thread per packed word (8 codes along K of one row).
 template <bool BF16, int ZMODE>
 __global__ void __launch_bounds__(256) dequant_kernel(const uint32_t *__restrict__ qw,

@@ -13,20 +13,23 @@ from typing import Optional
 import torch
 
 from . import _lib
-from ._lib import (QF_BF16, QF_F16, QF_F32, QF_LAYOUT_CANONICAL, QF_LAYOUT_INTERLEAVED, QF_LAYOUT_TILED, QF_PATH_AUTO,
-                   QF_PATH_GEMV, QF_ZERO_CONST, QF_ZERO_I8, QF_ZERO_U4, LinearDesc, QuantForgeError)
+from ._lib import (QF_BF16, QF_EPI_NONE, QF_EPI_RESIDUAL_ADD, QF_EPI_SILU_MUL, QF_F16, QF_F32, QF_LAYOUT_CANONICAL,
+                   QF_LAYOUT_GEMV_SLAB, QF_LAYOUT_INTERLEAVED, QF_LAYOUT_TILED, QF_PATH_AUTO, QF_PATH_GEMV,
+                   QF_SLAB_MAX_M, QF_ZERO_CONST, QF_ZERO_I8, QF_ZERO_U4, LinearDesc, QuantForgeError)
 
 _DT = {torch.float16: QF_F16, torch.bfloat16: QF_BF16, torch.float32: QF_F32}
 _ctxs: dict[int, ctypes.c_void_p] = {}
-_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_workspaces: dict[tuple[int, int], list] = {}
 
 
 def _ctx(device: torch.device) -> ctypes.c_void_p:
+    """The runtime context of `device` (created on first use; the caller's current device is left as it is)."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
     if idx not in _ctxs:
         lib = _lib.load()
         h = ctypes.c_void_p()
-        st = lib.qf_ctx_create(ctypes.byref(h), idx)
+        with torch.cuda.device(idx):
+            st = lib.qf_ctx_create(ctypes.byref(h), idx)
         if st != 0:
             raise QuantForgeError(st, _lib.status_name(st), f"qf_ctx_create(device={idx}) failed")
         _ctxs[idx] = h
@@ -111,7 +114,7 @@ def unpack_int4(packed: torch.Tensor) -> torch.Tensor:
 # linear
 # --------------------------------------------------------------------------------------------
 def _make_desc(M, N, K, group_size, act_dtype, out_dtype, zeros, zero_const, path, split_k,
-               weight_layout=QF_LAYOUT_CANONICAL) -> LinearDesc:
+               weight_layout=QF_LAYOUT_CANONICAL, epilogue=QF_EPI_NONE) -> LinearDesc:
     d = LinearDesc()
     d.M, d.N, d.K = M, N, K
     d.group_size = group_size
@@ -128,6 +131,7 @@ def _make_desc(M, N, K, group_size, act_dtype, out_dtype, zeros, zero_const, pat
     d.path = path
     d.split_k = split_k
     d.weight_layout = weight_layout
+    d.epilogue = epilogue
     return d
 
 
@@ -136,15 +140,20 @@ def workspace_bytes(desc: LinearDesc) -> int:
 
 
 def _workspace(dev: torch.device, nbytes: int) -> Optional[torch.Tensor]:
-    """Per (device, stream) zero-initialised scratch, grown on demand. Calls on one stream are ordered."""
+    """Per (device, stream) zero-initialised scratch. Calls on one stream are ordered, so they share it.
+
+    A call that needs more than any buffer made so far gets a NEW, larger buffer; the older ones stay alive and
+    keep serving the smaller requests, because a CUDA graph captured earlier still holds their addresses."""
     if nbytes == 0:
         return None
     key = (dev.index if dev.index is not None else torch.cuda.current_device(),
            torch.cuda.current_stream(dev).cuda_stream)
-    ws = _workspaces.get(key)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
-        _workspaces[key] = ws
+    bufs = _workspaces.setdefault(key, [])
+    for ws in bufs:  # ascending sizes: the smallest buffer that fits, the same one every time for a given size
+        if ws.numel() >= nbytes:
+            return ws
+    ws = torch.zeros(max(nbytes, 4 << 20), dtype=torch.uint8, device=dev)
+    bufs.append(ws)
     return ws
 
 
@@ -174,34 +183,144 @@ def _check_linear_tensors(x, qweight, scales, zeros, group_size):
     return M, N, K
 
 
-def w4a16_linear(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor] = None,
+class SlabWeight:
+    """Weights of one linear in QF_LAYOUT_GEMV_SLAB (codes, scales and zeros in one blob) and the facts needed to
+    call the streaming GEMV kernel on them. Made by `prepack_gemv_slab`; serves batches of up to 32 rows."""
+
+    def __init__(self, blob: torch.Tensor, N: int, K: int, group_size: int, act_dtype: torch.dtype, zero_mode: int,
+                 zero_const: int):
+        self.blob, self.N, self.K, self.group_size = blob, N, K, group_size
+        self.act_dtype, self.zero_mode, self.zero_const = act_dtype, zero_mode, zero_const
+
+    @property
+    def device(self):
+        return self.blob.device
+
+
+def prepack_gemv_slab(qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor] = None,
+                      group_size: int = 128, zero_const: int = 8) -> SlabWeight:
+    """One-time prepack of canonical weights (+ scales, zeros) for the streaming GEMV kernel (M <= 32)."""
+    dev = _need_cuda(qweight, scales, zeros)
+    N = qweight.shape[0]
+    K = qweight.shape[1] * (8 if qweight.dtype == torch.int32 else 2)
+    d = _make_desc(1, N, K, group_size, scales.dtype, scales.dtype, zeros, zero_const, QF_PATH_AUTO, 0,
+                   QF_LAYOUT_GEMV_SLAB)
+    lib = _lib.load()
+    nbytes = int(lib.qf_prepack_bytes(QF_LAYOUT_GEMV_SLAB, N, K))
+    if nbytes == 0:
+        raise ValueError("QF_LAYOUT_GEMV_SLAB needs N % 64 == 0 and K % 128 == 0")
+    qweight, scales = qweight.contiguous(), scales.contiguous()
+    zeros = zeros.contiguous() if zeros is not None else None
+    blob = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    ctx = _ctx(dev)
+    with torch.cuda.device(dev):
+        st = lib.qf_prepack_gemv_slab(ctx, ctypes.byref(d), _ptr(qweight), _ptr(scales), _ptr(zeros), _ptr(blob),
+                                      _stream(dev))
+    _check(st, ctx)
+    return SlabWeight(blob, N, K, group_size, scales.dtype, d.zero_mode, int(zero_const))
+
+
+def unpack_gemv_slab(w: SlabWeight) -> torch.Tensor:
+    """The codes of a slab blob back as canonical int8 [N, K/2] (the inverse permutation of the prepack)."""
+    out = torch.empty((w.N, w.K // 2), dtype=torch.int8, device=w.device)
+    ctx = _ctx(w.device)
+    with torch.cuda.device(w.device):
+        st = _lib.load().qf_unpack_gemv_slab(ctx, w.N, w.K, _ptr(w.blob), _ptr(out), _stream(w.device))
+    _check(st, ctx)
+    return out
+
+
+def repack_kn_to_canonical(w_kn: torch.Tensor, K: int, N: int) -> torch.Tensor:
+    """W[K, N] as the reference's compiler half lays it out - int8 [K, N] (one code per byte) or int8 [K, N/2]
+    (two codes per byte along N) - to the canonical int8 [N, K/2] the kernels read."""
+    dev = _need_cuda(w_kn)
+    if tuple(w_kn.shape) == (K, N):
+        packed = 0
+    elif tuple(w_kn.shape) == (K, N // 2):
+        packed = 1
+    else:
+        raise ValueError(f"w_kn must be [{K}, {N}] or [{K}, {N // 2}], got {tuple(w_kn.shape)}")
+    w_kn = w_kn.contiguous()
+    out = torch.empty((N, K // 2), dtype=torch.int8, device=dev)
+    ctx = _ctx(dev)
+    with torch.cuda.device(dev):
+        st = _lib.load().qf_repack_kn_to_canonical(ctx, _ptr(w_kn), packed, K, N, _ptr(out), _stream(dev))
+    _check(st, ctx)
+    return out
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, dim: int = 0) -> torch.Tensor:
+    """Row order QF_EPI_SILU_MUL expects: groups of 8 gate rows followed by the matching 8 up rows, along `dim`
+    (dim 0 for qweight [N, ...], the last dim for scales / int8 zeros [G, N])."""
+    if gate.shape != up.shape or gate.shape[dim] % 8 != 0:
+        raise ValueError("gate and up must have the same shape, a multiple of 8 long along `dim`")
+    g = gate.movedim(dim, 0)
+    u = up.movedim(dim, 0)
+    n = g.shape[0]
+    both = torch.stack([g.reshape(n // 8, 8, *g.shape[1:]), u.reshape(n // 8, 8, *u.shape[1:])], dim=1)
+    return both.reshape(2 * n, *g.shape[1:]).movedim(0, dim).contiguous()
+
+
+def w4a16_linear(x: torch.Tensor, qweight, scales: Optional[torch.Tensor] = None,
+                 zeros: Optional[torch.Tensor] = None,
                  group_size: int = 128, zero_const: int = 8, out_dtype: Optional[torch.dtype] = None,
                  path: int = QF_PATH_AUTO, split_k: int = 0, out: Optional[torch.Tensor] = None,
-                 weight_layout: int = QF_LAYOUT_CANONICAL) -> torch.Tensor:
+                 weight_layout: int = QF_LAYOUT_CANONICAL, epilogue: int = QF_EPI_NONE,
+                 residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Y[M,N] = X[M,K] . dequant(unpack(qweight))^T, fp32 accumulation, W never materialised.
 
     weight_layout: QF_LAYOUT_CANONICAL, or QF_LAYOUT_INTERLEAVED for weights passed through prepack_w4.
+    qweight may also be a `SlabWeight` (prepack_gemv_slab): scales / zeros / group_size / weight_layout then come
+    from it.
+    epilogue: QF_EPI_SILU_MUL (weights are gate|up rows interleaved by `interleave_gate_up`; Y is [M, N/2]) or
+    QF_EPI_RESIDUAL_ADD (Y = X.W^T + residual; residual [M, N] of out_dtype, may be `out` itself).
 
     x        f16|bf16 [M, K]
     qweight  int8 [N, K/2] (two codes per byte along K) or int32 [N, K/8]
     scales   same dtype as x, [K/group_size, N]
     zeros    None (constant `zero_const`), int8 [G, N] or packed int32 [G, N/8] (pack_zeros_u4)
     """
-    dev = _need_cuda(x, qweight, scales, zeros)
-    M, N, K = _check_linear_tensors(x, qweight, scales, zeros, group_size)
+    if isinstance(qweight, SlabWeight):
+        w = qweight
+        dev = _need_cuda(x, w.blob, residual)
+        if x.dim() != 2 or x.shape[1] != w.K:
+            raise ValueError(f"x must be [M, {w.K}]")
+        if x.dtype != w.act_dtype:
+            raise TypeError("x must have the dtype the slab was built for")
+        M, N, K = x.shape[0], w.N, w.K
+        d = LinearDesc()
+        d.M, d.N, d.K, d.group_size = M, N, K, w.group_size
+        d.act_dtype, d.zero_mode, d.zero_const = _DT[x.dtype], w.zero_mode, w.zero_const
+        d.path, d.split_k, d.weight_layout, d.epilogue = QF_PATH_AUTO, split_k, QF_LAYOUT_GEMV_SLAB, epilogue
+        ptr_w, ptr_s, ptr_z = _ptr(w.blob), _ptr(None), _ptr(None)
+        x = x.contiguous()
+    else:
+        if scales is None:
+            raise ValueError("scales are required unless qweight is a SlabWeight")
+        dev = _need_cuda(x, qweight, scales, zeros, residual)
+        M, N, K = _check_linear_tensors(x, qweight, scales, zeros, group_size)
+        x, qweight, scales = x.contiguous(), qweight.contiguous(), scales.contiguous()
+        zeros = zeros.contiguous() if zeros is not None else None
+        d = _make_desc(M, N, K, group_size, x.dtype, x.dtype, zeros, zero_const, path, split_k, weight_layout,
+                       epilogue)
+        ptr_w, ptr_s, ptr_z = _ptr(qweight), _ptr(scales), _ptr(zeros)
     out_dtype = out_dtype or x.dtype
-    x, qweight, scales = x.contiguous(), qweight.contiguous(), scales.contiguous()
-    zeros = zeros.contiguous() if zeros is not None else None
+    d.out_dtype = _DT[out_dtype]
+    shape = (M, N // 2) if epilogue == QF_EPI_SILU_MUL else (M, N)
     if out is None:
-        out = torch.empty((M, N), dtype=out_dtype, device=dev)
-    elif tuple(out.shape) != (M, N) or out.dtype != out_dtype or not out.is_contiguous():
-        raise ValueError("out must be a contiguous [M, N] tensor of out_dtype")
-    d = _make_desc(M, N, K, group_size, x.dtype, out_dtype, zeros, zero_const, path, split_k, weight_layout)
+        out = torch.empty(shape, dtype=out_dtype, device=dev)
+    elif tuple(out.shape) != shape or out.dtype != out_dtype or not out.is_contiguous():
+        raise ValueError(f"out must be a contiguous {list(shape)} tensor of out_dtype")
+    if epilogue == QF_EPI_RESIDUAL_ADD:
+        if residual is None or tuple(residual.shape) != shape or residual.dtype != out_dtype or \
+                not residual.is_contiguous():
+            raise ValueError("QF_EPI_RESIDUAL_ADD needs a contiguous residual of the output's shape and dtype")
     ctx = _ctx(dev)
     with torch.cuda.device(dev):
         ws = _workspace(dev, workspace_bytes(d))
-        st = _lib.load().qf_w4a16_linear(ctx, ctypes.byref(d), _ptr(x), _ptr(qweight), _ptr(scales), _ptr(zeros),
-                                         _ptr(out), _ptr(ws), ws.numel() if ws is not None else 0, _stream(dev))
+        st = _lib.load().qf_w4a16_linear_fused(ctx, ctypes.byref(d), _ptr(x), ptr_w, ptr_s, ptr_z, _ptr(out),
+                                               _ptr(residual), _ptr(ws), ws.numel() if ws is not None else 0,
+                                               _stream(dev))
     _check(st, ctx)
     return out
 

@@ -1,6 +1,6 @@
 """Run one W4A16 linear configuration on the GPU and print its device time (for profiling a single kernel).
 
-    python -m quantforge_b200.run_case --M 1 --K 4096 --N 14336 --act bf16 [--iters 5] [--copies 6] [--sym]
+    python run_case.py --M 1 --K 4096 --N 14336 --act bf16 [--iters 5] [--copies 6] [--sym]
 
 Inputs are seeded synthetic tensors (uniform uint4 codes, |N(0,0.02)|/7 scales, uniform uint4 zeros or the
 constant 8 with --sym, N(0,1) activations).  `--copies` weight sets are rotated so that, with copies x weight
@@ -43,6 +43,8 @@ def main():
     ap.add_argument("--split-k", type=int, default=0)
     ap.add_argument("--interleaved", action="store_true", help="prepack the weights (QF_LAYOUT_INTERLEAVED)")
     ap.add_argument("--tiled", action="store_true", help="prepack the weights (QF_LAYOUT_TILED)")
+    ap.add_argument("--slab", action="store_true",
+                    help="prepack weights, scales and zeros for the streaming GEMV kernel (QF_LAYOUT_GEMV_SLAB)")
     ap.add_argument("--graph", action="store_true",
                     help="time a CUDA graph of one launch per weight copy instead of single launches")
     args = ap.parse_args()
@@ -61,10 +63,16 @@ def main():
     if args.tiled:
         sets = [(qf.prepack_w4(qw, layout=2), sc, zr, x) for (qw, sc, zr, x) in sets]
         layout = 2
+    if args.slab:
+        sets = [(qf.prepack_gemv_slab(qw, sc, zr, 128, 8), None, None, x) for (qw, sc, zr, x) in sets]
+        layout = 3
     y = torch.empty(args.M, args.N, dtype=out_dtype, device=dev)
 
     def launch(i):
         qw, sc, zr, x = sets[i % args.copies]
+        if args.slab:
+            qf.w4a16_linear(x, qw, out_dtype=out_dtype, split_k=args.split_k, out=y)
+            return
         qf.w4a16_linear(x, qw, sc, zr, group_size=128, zero_const=8, out_dtype=out_dtype, path=path,
                         split_k=args.split_k, out=y, weight_layout=layout)
 

@@ -41,7 +41,12 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
     ctx = ops._ctx(dev)
     stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
-    for call, (M, K, N, split_k, seed) in enumerate([(3, 2048, 512, 4, 21), (8, 4096, 1024, 0, 22)]):
+    # Plans with more than 8 splits, or more than 8 chunks of K per split, cannot sum their splits inside a
+    # thread-block cluster: their partial sums really travel through the static array (the first two cases; the
+    # other two take the cluster route and only have the array's counters cleared).
+    cases = [(1, 14336, 4096, 0, 20), (2, 4096, 512, 12, 23), (3, 2048, 512, 4, 21), (8, 4096, 1024, 0, 22)]
+    used_scratch = 0
+    for call, (M, K, N, split_k, seed) in enumerate(cases):
         d = O.make_inputs(M=M, K=K, N=N, group_size=128, act_dtype="bf16", seed=seed)
         x = torch.from_numpy(d["x"]).to(torch.bfloat16).to(dev)
         qw = torch.from_numpy(d["qweight"]).to(dev)
@@ -50,7 +55,12 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
         desc = _desc(_lib, M, N, K, split_k)
 
         ws_bytes = lib.qf_w4a16_workspace_bytes(ctypes.byref(desc))
-        assert ws_bytes > 0, "the case must exercise the split-K scratch"
+        assert ws_bytes > 0, "the case must be a split-K plan"
+        path, split = ctypes.c_int32(), ctypes.c_int32()
+        assert lib.qf_w4a16_plan(ctypes.byref(desc), ctypes.byref(path), ctypes.byref(split)) == 0
+        chunks_per_split = -(-(K // 128) // split.value)
+        if split.value > 8 or chunks_per_split > 8:
+            used_scratch += 1
         ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=dev)
         y_ref = torch.full((M, N), float("nan"), dtype=torch.float32, device=dev)
         st = lib.qf_w4a16_linear(ctx, ctypes.byref(desc), _vp(x), _vp(qw), _vp(sc), _vp(zr), _vp(y_ref), _vp(ws),
@@ -67,6 +77,7 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
         assert O.rel_err(y.cpu().numpy(), y_ref.cpu().numpy()) < 1e-4, f"call {call}"
         want = O.w4a16_linear(d["x"], d["qweight"], d["scales"], d["zeros"], 128, "bf16", O.F32, accumulate="f64")
         assert O.rel_err(y.cpu().numpy(), want) < 1e-4, f"call {call} vs oracle"
+    assert used_scratch >= 2, "at least two of the calls must keep their partial sums in the static array"
 
 
 def test_static_scratch_rejects_oversized_requests():
