@@ -44,6 +44,11 @@ def num_threads() -> int:
     return int(lib().qfo_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    """Thread count of the following calls (torchrun exports OMP_NUM_THREADS=1 to its children)."""
+    lib().qfo_set_num_threads(ctypes.c_int(int(n)))
+
+
 def _p(a: np.ndarray):
     return a.ctypes.data_as(ctypes.c_void_p)
 

@@ -71,6 +71,15 @@ int qfo_num_threads(void) {
 #endif
 }
 
+/* Sets the thread count of the following calls (a launcher may have exported OMP_NUM_THREADS=1). */
+void qfo_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* out[r, 2i] = b & 0xF ; out[r, 2i+1] = (b >> 4) & 0xF on the raw byte. */
 void qfo_unpack_int4(const uint8_t *packed, int8_t *out, int64_t rows, int64_t packed_cols) {
 #pragma omp parallel for schedule(static)

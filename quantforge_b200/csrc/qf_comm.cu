@@ -2,7 +2,10 @@
 // (CUDA IPC within one node, NVLink peer access), and the GEMV kernel sums the partial outputs across GPUs
 // in its own epilogue (qf_gemv.cu, AR instantiations). Nothing here runs in the hot call except building
 // the kernel's pointer table from the already mapped buffers.
+#include <cstdlib>
 #include <cstring>
+#include <mutex>
+#include <vector>
 
 #include "qf_common.cuh"
 
@@ -14,11 +17,24 @@ struct qf_comm {
     size_t bytes = 0;
     void *local = nullptr;
     void *peer[qf::kMaxPeers] = {nullptr};
+    bool peer_is_ipc[qf::kMaxPeers] = {false};  // mapped with cudaIpcOpenMemHandle (to be closed), not a same-process buffer
     bool connected = false;
+    long long wait_cycles = 0;
     cudaIpcMemHandle_t handle;
 };
 
 namespace qf {
+
+// Exchange buffers created by THIS process, by handle: an IPC handle cannot be opened in the process that made it,
+// so a process that drives several ranks (one thread per GPU, or a test that plays two ranks) gets the pointer from
+// here, with peer access enabled when the buffer lives on another GPU.
+struct LocalBuffer {
+    cudaIpcMemHandle_t handle;
+    void *ptr;
+    int device;
+};
+static std::mutex g_local_mutex;
+static std::vector<LocalBuffer> g_local_buffers;
 
 static ArParams comm_params(const qf_comm *c) {
     ArParams ar = {};
@@ -30,6 +46,7 @@ static ArParams comm_params(const qf_comm *c) {
     ar.slot_elems = c->slot_elems;
     ar.world = c->world;
     ar.rank = c->rank;
+    ar.wait_cycles = c->wait_cycles;
     return ar;
 }
 
@@ -46,7 +63,8 @@ int qf_comm_create(qf_ctx *ctx, int rank, int world, size_t max_out_elems, qf_co
         return fail(ctx, QF_ERR_BAD_ARG, "qf_comm_create: need 1 <= world <= 8 and 0 <= rank < world");
     if (max_out_elems == 0) return fail(ctx, QF_ERR_BAD_ARG, "qf_comm_create: max_out_elems must be positive");
     if (!ctx->dev_status) return fail(ctx, QF_ERR_CUDA, "context has no device status word");
-    QF_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    DeviceGuard guard(ctx->device);
+    if (!guard.ok()) return fail(ctx, QF_ERR_CUDA, "cannot make the context's device current");
     qf_comm *c = new (std::nothrow) qf_comm();
     if (!c) return fail(ctx, QF_ERR_CUDA, "out of host memory");
     c->ctx = ctx;
@@ -65,6 +83,17 @@ int qf_comm_create(qf_ctx *ctx, int rank, int world, size_t max_out_elems, qf_co
     }
     c->peer[rank] = c->local;
     c->connected = (world == 1);
+    // How long a collect waits for its peers. QF_EXCHANGE_WAIT_MS shortens it (tests of the time-out path); the
+    // conversion assumes the 1.9 GHz the SM clock counter runs at under load.
+    c->wait_cycles = kExchangeWaitCycles;
+    if (const char *e = std::getenv("QF_EXCHANGE_WAIT_MS")) {
+        const long long ms = std::atoll(e);
+        if (ms > 0) c->wait_cycles = ms * 1900000LL;
+    }
+    if (world > 1) {
+        std::lock_guard<std::mutex> g(g_local_mutex);
+        g_local_buffers.push_back(LocalBuffer{c->handle, c->local, ctx->device});
+    }
     *out = c;
     return QF_OK;
 }
@@ -86,14 +115,34 @@ int qf_comm_connect(qf_comm *comm, const void *handles, int n_handles) {
     if (comm->connected) return QF_OK;
     if (!handles || n_handles != comm->world)
         return fail(ctx, QF_ERR_BAD_ARG, "qf_comm_connect: one handle per rank, in rank order");
-    QF_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    DeviceGuard guard(ctx->device);
+    if (!guard.ok()) return fail(ctx, QF_ERR_CUDA, "cannot make the context's device current");
     for (int r = 0; r < comm->world; ++r) {
         if (r == comm->rank) continue;
         cudaIpcMemHandle_t h;
         memcpy(&h, (const char *)handles + (size_t)r * QF_COMM_HANDLE_BYTES, QF_COMM_HANDLE_BYTES);
         void *ptr = nullptr;
-        cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
-        if (e != cudaSuccess) return cuda_fail(ctx, e, "qf_comm_connect: cudaIpcOpenMemHandle");
+        int owner_device = -1;
+        {
+            std::lock_guard<std::mutex> g(g_local_mutex);
+            for (const LocalBuffer &lb : g_local_buffers)
+                if (memcmp(&lb.handle, &h, sizeof(h)) == 0) {
+                    ptr = lb.ptr;
+                    owner_device = lb.device;
+                }
+        }
+        if (ptr) {
+            // a buffer of this very process
+            if (owner_device != ctx->device) {
+                const cudaError_t pe = cudaDeviceEnablePeerAccess(owner_device, 0);
+                if (pe == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+                else if (pe != cudaSuccess) return cuda_fail(ctx, pe, "qf_comm_connect: cudaDeviceEnablePeerAccess");
+            }
+        } else {
+            cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) return cuda_fail(ctx, e, "qf_comm_connect: cudaIpcOpenMemHandle");
+            comm->peer_is_ipc[r] = true;
+        }
         comm->peer[r] = ptr;
     }
     comm->connected = true;
@@ -102,9 +151,17 @@ int qf_comm_connect(qf_comm *comm, const void *handles, int n_handles) {
 
 int qf_comm_destroy(qf_comm *comm) {
     if (!comm) return QF_OK;
-    cudaSetDevice(comm->ctx->device);
+    DeviceGuard guard(comm->ctx->device);
     for (int r = 0; r < comm->world; ++r)
-        if (r != comm->rank && comm->peer[r]) cudaIpcCloseMemHandle(comm->peer[r]);
+        if (r != comm->rank && comm->peer[r] && comm->peer_is_ipc[r]) cudaIpcCloseMemHandle(comm->peer[r]);
+    {
+        std::lock_guard<std::mutex> g(g_local_mutex);
+        for (size_t i = 0; i < g_local_buffers.size(); ++i)
+            if (g_local_buffers[i].ptr == comm->local) {
+                g_local_buffers.erase(g_local_buffers.begin() + (long)i);
+                break;
+            }
+    }
     if (comm->local) cudaFree(comm->local);
     delete comm;
     return QF_OK;
@@ -123,17 +180,33 @@ static int linear_exchange(qf_ctx *ctx, qf_comm *comm, const qf_linear_desc *des
         return fail(ctx, QF_ERR_UNSUPPORTED,
                     "the in-kernel exchange serves M <= 64; larger batches are bandwidth-bound on the links and "
                     "should follow the linear with a bulk collective");
+    if (desc->epilogue != QF_EPI_NONE)
+        return fail(ctx, QF_ERR_UNSUPPORTED, "the exchanging linears take no fused epilogue");
+    qf_linear_desc local_desc = *desc;
+    if (local_desc.weight_layout == QF_LAYOUT_GEMV_SLAB && local_desc.split_k == 0) {
+        // A collecting thread block waits for its peers while it holds its SM slot, so every thread block of the
+        // launch must be resident at once on every rank: two per SM always fit (registers, shared memory).
+        local_desc.split_k = 2 * ctx->sm_count;
+        desc = &local_desc;
+    }
     Plan plan;
     std::string why;
     int st = make_plan(desc, &plan, &why);
     if (st != QF_OK) return fail(ctx, st, why);
     if (desc->M == 0) return QF_OK;
-    if (!X || !qweight || !scales || !Y) return fail(ctx, QF_ERR_BAD_ARG, "null tensor pointer");
-    if (desc->zero_mode != QF_ZERO_CONST && !qzeros_or_null)
+    st = check_current_device(ctx);
+    if (st != QF_OK) return st;
+    const bool slab = desc->weight_layout == QF_LAYOUT_GEMV_SLAB;
+    if (!X || !qweight || (!slab && !scales) || !Y) return fail(ctx, QF_ERR_BAD_ARG, "null tensor pointer");
+    if (!slab && desc->zero_mode != QF_ZERO_CONST && !qzeros_or_null)
         return fail(ctx, QF_ERR_BAD_ARG, "zero_mode needs a qzeros tensor");
     auto al16 = [](const void *p) { return ((uintptr_t)p & 15u) == 0; };
-    if (!al16(X) || !al16(qweight) || !al16(scales) || !al16(Y) || (qzeros_or_null && !al16(qzeros_or_null)))
+    if (!al16(X) || !al16(qweight) || !al16(Y) ||
+        (!slab && (!al16(scales) || (qzeros_or_null && !al16(qzeros_or_null)))))
         return fail(ctx, QF_ERR_BAD_ARG, "device pointers must be 16-byte aligned");
+    if (slab && desc->split_k > 0 && desc->split_k > 4 * ctx->sm_count)
+        return fail(ctx, QF_ERR_UNSUPPORTED,
+                    "an exchanging launch must be resident at once: at most 4 thread blocks per SM");
     if ((size_t)desc->M * (size_t)desc->N > comm->slot_elems)
         return fail(ctx, QF_ERR_WORKSPACE, "M*N exceeds the max_out_elems this comm was created with");
     const size_t need = plan.ws_partial_bytes + plan.ws_counter_bytes;
@@ -144,6 +217,8 @@ static int linear_exchange(qf_ctx *ctx, qf_comm *comm, const qf_linear_desc *des
     }
     ArParams ar = comm_params(comm);
     ar.gather = gather;
+    if (plan.slab)
+        return launch_gemv_slab_ar(ctx, desc, plan, X, qweight, Y, workspace, (cudaStream_t)stream, ar);
     if (plan.path == QF_PATH_GEMV)
         return launch_gemv_ar(ctx, desc, plan, X, qweight, scales, qzeros_or_null, Y, workspace,
                               (cudaStream_t)stream, ar);

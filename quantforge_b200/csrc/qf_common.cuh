@@ -176,6 +176,7 @@ struct ArParams {
     int world;
     int rank;
     int gather;                   // 0: Y[M, N] = sum over ranks; 1: Y[M, world*N], columns [r*N, (r+1)*N) from rank r
+    long long wait_cycles;        // SM clocks a collect waits for the peers before it gives up (QF_ERR_TIMEOUT)
 };
 
 // Kernel argument of the exchange: an ArParams in the exchanging instantiations, an empty struct in the plain ones.
@@ -213,6 +214,8 @@ void slab_geometry(int64_t M, int64_t N, int64_t K, int sm_count, int grid_reque
 size_t slab_workspace_bytes(int grid, int64_t M);
 int launch_gemv_slab(qf_ctx *ctx, const qf_linear_desc *d, const Plan &p, const void *X, const void *blob, void *Y,
                      const void *residual, void *ws, cudaStream_t s);
+int launch_gemv_slab_ar(qf_ctx *ctx, const qf_linear_desc *d, const Plan &p, const void *X, const void *blob,
+                        void *Y, void *ws, cudaStream_t s, const ArParams &ar);
 int launch_slab_prepack(qf_ctx *ctx, const qf_linear_desc *d, const void *qw, const void *scales, const void *zeros,
                         void *blob, cudaStream_t s);
 int launch_slab_unpack(qf_ctx *ctx, int64_t N, int64_t K, const void *blob, void *qw, cudaStream_t s);
@@ -488,7 +491,7 @@ __device__ __forceinline__ bool exch_collect_tile_impl(const ArParams &ar, unsig
                     if (valid[j] && r < ar.world && (v[j][r].y != token || v[j][r].w != token)) miss = true;
             if (!miss) break;
             __nanosleep(100);
-            if (clock64() - t0 > kExchangeWaitCycles || *fail) return false;
+            if (clock64() - t0 > ar.wait_cycles || *fail) return false;
 #pragma unroll
             for (int j = 0; j < U; ++j)
 #pragma unroll

@@ -123,8 +123,81 @@ __device__ __forceinline__ void slab_store(const SlabParams &p, int64_t n0, int 
         }
 }
 
-template <bool BF16, int MT>
-__global__ void __launch_bounds__(SLAB_THREADS) gemv_slab_kernel(const SlabParams p) {
+// The cross-GPU step of the exchanging instantiations (row-parallel sum / column-parallel gather over NVLink peer
+// memory, qf_w4a16_linear_allreduce / _allgather). A warp pushes every tile it finishes to all ranks at once, as
+// (value, token) words, while its thread block keeps streaming; at the very end of the block's life it collects the
+// other ranks' words for the tiles it finished - by then they have usually arrived - and writes Y.
+template <int MT>
+__device__ __forceinline__ void slab_push(const SlabParams &p, const ArParams &ar, unsigned epoch, int64_t n0, int g,
+                                          int t, const float (&v)[MT][4]) {
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int64_t m = nt * 8 + 2 * t + e;
+            if (m < p.M) {
+                exch_push(ar, epoch, (size_t)(m * p.N + n0 + g), v[nt][e]);
+                exch_push(ar, epoch, (size_t)(m * p.N + n0 + g + 8), v[nt][2 + e]);
+            }
+        }
+}
+// Collects the 16 x M tile at weight rows n0.. from every rank's slot and writes it (sum in rank order, or each
+// rank's values into its own column range). All 32 lanes call it; returns false when a wait ran out.
+template <int MT>
+__device__ __forceinline__ bool slab_collect(const SlabParams &p, const ArParams &ar, unsigned epoch, int64_t n0,
+                                             int g, int t, volatile int *abort_flag) {
+    const unsigned token = epoch + 1u;
+    const uint2 *base = ar.local_slots + exch_parity_offset(ar, epoch);
+    const long long t0 = clock64();
+#pragma unroll 1
+    for (int q = 0; q < MT * 2; ++q) {
+        const int64_t m = (q >> 1) * 8 + 2 * t + (q & 1);
+        const bool valid = m < p.M;
+        const size_t ea = (size_t)(m * p.N + n0 + g), eb = ea + 8;
+        uint2 va[kMaxPeers], vb[kMaxPeers];
+        while (true) {
+            bool miss = false;
+            if (valid) {
+#pragma unroll
+                for (int r = 0; r < kMaxPeers; ++r)
+                    if (r < ar.world) {
+                        va[r] = ld_pair_sys(base + (size_t)r * ar.slot_elems + ea);
+                        vb[r] = ld_pair_sys(base + (size_t)r * ar.slot_elems + eb);
+                    }
+#pragma unroll
+                for (int r = 0; r < kMaxPeers; ++r)
+                    if (r < ar.world && (va[r].y != token || vb[r].y != token)) miss = true;
+            }
+            if (!__any_sync(0xffffffffu, miss)) break;
+            __nanosleep(100);
+            if (__any_sync(0xffffffffu, clock64() - t0 > ar.wait_cycles || *abort_flag != 0)) return false;
+        }
+        if (!valid) continue;
+        if (ar.gather) {
+            const int64_t row = m * (p.N * ar.world) + n0 + g;
+#pragma unroll
+            for (int r = 0; r < kMaxPeers; ++r)
+                if (r < ar.world) {
+                    store_out(p.Y, p.out_dtype, row + (int64_t)r * p.N, __uint_as_float(va[r].x));
+                    store_out(p.Y, p.out_dtype, row + (int64_t)r * p.N + 8, __uint_as_float(vb[r].x));
+                }
+        } else {
+            float sa = 0.f, sb = 0.f;
+#pragma unroll
+            for (int r = 0; r < kMaxPeers; ++r)
+                if (r < ar.world) {
+                    sa += __uint_as_float(va[r].x);
+                    sb += __uint_as_float(vb[r].x);
+                }
+            store_out(p.Y, p.out_dtype, m * p.N + n0 + g, sa);
+            store_out(p.Y, p.out_dtype, m * p.N + n0 + g + 8, sb);
+        }
+    }
+    return true;
+}
+
+template <bool BF16, int MT, bool EXCH>
+__device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typename ExchArg<EXCH>::type &ar) {
     extern __shared__ __align__(128) uint8_t slab_smem[];
     __shared__ int s_abort;
 
@@ -177,10 +250,12 @@ __global__ void __launch_bounds__(SLAB_THREADS) gemv_slab_kernel(const SlabParam
             if (++c == p.chunks) c = 0;
         }
         issued = npre;
+        // steady state: ring position advances incrementally (npre == depth whenever this loop runs)
+        int s = 0;
+        uint32_t ph = 0;  // parity of the consumers' previous pass over stage s
         for (int it = npre; it < n_units; ++it) {
-            const int s = it % p.depth;
-            const uint32_t ph = (uint32_t)((it / p.depth) - 1) & 1u;
-            const bool ok = mbar_wait(empty_bar(s), ph, abort_flag);
+            bool ok = mbar_try_wait(empty_bar(s), ph) != 0;
+            if (!ok) ok = mbar_wait(empty_bar(s), ph, abort_flag);
             if (!__all_sync(0xffffffffu, ok)) break;
             if (lane == 0) {
                 mbar_arrive_expect_tx(full_bar(s), tx);
@@ -192,6 +267,10 @@ __global__ void __launch_bounds__(SLAB_THREADS) gemv_slab_kernel(const SlabParam
                           p.X + (size_t)lane * p.K + (size_t)c * 128, 256u, full_bar(s));
             if (++c == p.chunks) c = 0;
             issued = it + 1;
+            if (++s == p.depth) {
+                s = 0;
+                ph ^= 1u;
+            }
         }
         if (s_abort) {
             // drain this block's own copies before its shared memory goes away (the consumers stopped waiting)
@@ -206,6 +285,10 @@ __global__ void __launch_bounds__(SLAB_THREADS) gemv_slab_kernel(const SlabParam
 
     // ------------------------------ consumers ------------------------------
     griddep_wait();  // nothing to compute before the activations exist; the bounded waits below start after it
+    // calls completed on this comm (same value on every rank): read after the previous call on this rank finished
+    unsigned ar_epoch = 0u;
+    if constexpr (EXCH) ar_epoch = exch_read_epoch(ar);
+    long long first_done = -1, last_done = -1;  // row blocks this warp finished during the stream (a contiguous run)
     const int g = lane >> 2;
     const int t = lane & 3;
     float acc[MT][2][4];
@@ -228,20 +311,34 @@ __global__ void __launch_bounds__(SLAB_THREADS) gemv_slab_kernel(const SlabParam
     unsigned long long *my_pairs = p.pairs + (((size_t)cta * 4 + warp) * MT) * 128 + lane * 4;
     bool aborted = false;
 
+    // Ring position and addresses advance incrementally (no division by the run-time depth in the loop).
+    int s = 0;
+    uint32_t ph = 0;
+    uint32_t fbar = full_bar(0), ebar = empty_bar(0);
+    uint32_t wptr = stage(0) + (uint32_t)warp * SLAB_TILE_BYTES + (uint32_t)lane * 16u;  // this lane's codes
+    const uint32_t cst_off = 1024u + (uint32_t)g * 4u - (uint32_t)lane * 16u;            // -> its row's constants
+    uint32_t x_off[MT];                                                                  // -> its activation rows
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt) {
+        // batch rows beyond m_pad are never stored: wrap into the rows the stage holds
+        const uint32_t row = (uint32_t)((nt * 8 + g) & (p.m_pad - 1));
+        x_off[nt] = (uint32_t)SLAB_UNIT_BYTES - (uint32_t)warp * SLAB_TILE_BYTES - (uint32_t)lane * 16u +
+                    (uint32_t)t * 16u + row * SLAB_X_PITCH;
+    }
+    const uint32_t wrap_back = (uint32_t)(p.depth - 1) * stage_bytes;
+
 #pragma unroll 1
     for (int it = 0; it < n_units; ++it) {
-        const int s = it % p.depth;
-        const bool ok = mbar_wait(full_bar(s), (uint32_t)(it / p.depth) & 1u, abort_flag);
+        bool ok = mbar_try_wait(fbar, ph) != 0;
+        if (!ok) ok = mbar_wait(fbar, ph, abort_flag);
         if (!__all_sync(0xffffffffu, ok)) {
             aborted = true;
             break;
         }
-        const uint32_t tile = stage(s) + (uint32_t)warp * SLAB_TILE_BYTES;
-        const uint4 va = lds128g(tile + (uint32_t)lane * 16u);
-        const uint4 vb = lds128g(tile + 512u + (uint32_t)lane * 16u);
-        const ZeroScale<BF16> za = slab_consts<BF16>(lds32g(tile + 1024u + (uint32_t)g * 4u));
-        const ZeroScale<BF16> zb = slab_consts<BF16>(lds32g(tile + 1024u + (uint32_t)(g + 8) * 4u));
-        const uint32_t xbase = stage(s) + SLAB_UNIT_BYTES + (uint32_t)t * 16u;
+        const uint4 va = lds128g(wptr);
+        const uint4 vb = lds128g(wptr + 512u);
+        const ZeroScale<BF16> za = slab_consts<BF16>(lds32g(wptr + cst_off));
+        const ZeroScale<BF16> zb = slab_consts<BF16>(lds32g(wptr + cst_off + 32u));
         const uint32_t wa[4] = {va.x, va.y, va.z, va.w};
         const uint32_t wb[4] = {vb.x, vb.y, vb.z, vb.w};
 #pragma unroll
@@ -251,15 +348,24 @@ __global__ void __launch_bounds__(SLAB_THREADS) gemv_slab_kernel(const SlabParam
             dequant8<BF16>(wb[j], zb, pb);
 #pragma unroll
             for (int nt = 0; nt < MT; ++nt) {
-                // batch rows beyond m_pad are never stored: wrap into the rows the stage holds
-                const uint32_t row = (uint32_t)((nt * 8 + g) & (p.m_pad - 1));
-                const uint4 xb = lds128g(xbase + row * SLAB_X_PITCH + (uint32_t)j * 64u);
+                const uint4 xb = lds128g(wptr + x_off[nt] + (uint32_t)j * 64u);
                 mma_16816<BF16>(acc[nt][0], pa[0], pb[0], pa[1], pb[1], xb.x, xb.y);
                 mma_16816<BF16>(acc[nt][1], pa[2], pb[2], pa[3], pb[3], xb.z, xb.w);
             }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(empty_bar(s));
+        if (lane == 0) mbar_arrive(ebar);
+        if (++s == p.depth) {
+            s = 0;
+            ph ^= 1u;
+            wptr -= wrap_back;
+            fbar = full_bar(0);
+            ebar = empty_bar(0);
+        } else {
+            wptr += stage_bytes;
+            fbar += 8u;
+            ebar += 8u;
+        }
         ++c;
         if (c == p.chunks || it == n_units - 1) {
             // end of this block's share of row block b
@@ -273,7 +379,13 @@ __global__ void __launch_bounds__(SLAB_THREADS) gemv_slab_kernel(const SlabParam
                     acc[nt][1][e] = 0.f;
                 }
             if (c_lo == 0 && c == p.chunks) {
-                slab_store<MT>(p, b * 64 + warp * 16, g, t, v);
+                if constexpr (EXCH) {
+                    slab_push<MT>(p, ar, ar_epoch, b * 64 + warp * 16, g, t, v);
+                    if (first_done < 0) first_done = b;
+                    last_done = b;
+                } else {
+                    slab_store<MT>(p, b * 64 + warp * 16, g, t, v);
+                }
             } else if (c == p.chunks) {
                 // this block owns row block b (it holds the end of its K range): finished at the very end
 #pragma unroll
@@ -357,12 +469,40 @@ __global__ void __launch_bounds__(SLAB_THREADS) gemv_slab_kernel(const SlabParam
                 }
         }
         if (!failed) {
-            slab_store<MT>(p, held_b * 64 + warp * 16, g, t, held);
-        } else if (lane == 0) {
-            *abort_flag = 1;
-            atomicExch(p.status, QF_ERR_TIMEOUT);
+            if constexpr (EXCH) slab_push<MT>(p, ar, ar_epoch, held_b * 64 + warp * 16, g, t, held);
+            else slab_store<MT>(p, held_b * 64 + warp * 16, g, t, held);
+        } else {
+            aborted = true;
+            if (lane == 0) {
+                *abort_flag = 1;
+                atomicExch(p.status, QF_ERR_TIMEOUT);
+            }
         }
     }
+    if constexpr (EXCH) {
+        // collect what this warp pushed: the row block finished last of all (the held one) and the full ones.
+        // A tile that this warp could not finish (abort) is still counted, so that the call's epoch advances.
+        const unsigned tiles_in_launch = (unsigned)(p.N >> 4);
+        bool ok = !aborted;
+        if (have_held) {
+            if (ok) ok = slab_collect<MT>(p, ar, ar_epoch, held_b * 64 + warp * 16, g, t, abort_flag);
+            if (lane == 0) exch_block_done(ar, ar_epoch, tiles_in_launch, !ok);
+        }
+        if (first_done >= 0)
+            for (long long bb = first_done; bb <= last_done; ++bb) {
+                if (ok) ok = slab_collect<MT>(p, ar, ar_epoch, bb * 64 + warp * 16, g, t, abort_flag);
+                if (lane == 0) exch_block_done(ar, ar_epoch, tiles_in_launch, !ok);
+            }
+    }
+}
+
+template <bool BF16, int MT>
+__global__ void __launch_bounds__(SLAB_THREADS) gemv_slab_kernel(const SlabParams p) {
+    gemv_slab_body<BF16, MT, false>(p, NoExchange{});
+}
+template <bool BF16, int MT>
+__global__ void __launch_bounds__(SLAB_THREADS) gemv_slab_exch_kernel(const SlabParams p, const ArParams ar) {
+    gemv_slab_body<BF16, MT, true>(p, ar);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -539,8 +679,12 @@ size_t slab_workspace_bytes(int grid, int64_t M) {
 
 template <bool BF16, int MT>
 static cudaError_t slab_set_attr() {
-    return cudaFuncSetAttribute(gemv_slab_kernel<BF16, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)(220u << 10));
+    cudaError_t e = cudaFuncSetAttribute(gemv_slab_kernel<BF16, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)(220u << 10));
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemv_slab_exch_kernel<BF16, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)(220u << 10));
+    return e;
 }
 
 int gemv_slab_init(qf_ctx *ctx) {
@@ -553,8 +697,9 @@ int gemv_slab_init(qf_ctx *ctx) {
     return QF_OK;
 }
 
-int launch_gemv_slab(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *blob, void *Y,
-                     const void *residual, void *ws, cudaStream_t s) {
+static int launch_gemv_slab_impl(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X,
+                                 const void *blob, void *Y, const void *residual, void *ws, cudaStream_t s,
+                                 const ArParams *ar) {
     SlabParams p;
     p.blob = (const uint8_t *)blob;
     p.X = (const uint16_t *)X;
@@ -570,13 +715,37 @@ int launch_gemv_slab(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, con
     p.depth = plan.chunks_per_split;
     p.m_pad = slab_m_pad(d->M);
     p.out_dtype = d->out_dtype;
-    p.epilogue = d->epilogue;
+    p.epilogue = ar ? QF_EPI_NONE : d->epilogue;
     const dim3 grid((unsigned)plan.split_k), blk(SLAB_THREADS);
     const size_t smem = slab_smem_bytes(p.depth, p.m_pad);
     const bool pdl = pdl_enabled();
     const int mt = (p.m_pad + 7) / 8;
+    const bool bf = d->act_dtype == QF_BF16;
     cudaError_t le;
-    if (d->act_dtype == QF_BF16) {
+    if (ar) {
+        // a thread block that collects waits for the peers' pushes while it holds its slot: the whole launch must be
+        // resident at once on every rank
+        int per_sm = 0;
+        const void *fn = bf ? (mt == 1   ? (const void *)gemv_slab_exch_kernel<true, 1>
+                               : mt == 2 ? (const void *)gemv_slab_exch_kernel<true, 2>
+                                         : (const void *)gemv_slab_exch_kernel<true, 4>)
+                            : (mt == 1   ? (const void *)gemv_slab_exch_kernel<false, 1>
+                               : mt == 2 ? (const void *)gemv_slab_exch_kernel<false, 2>
+                                         : (const void *)gemv_slab_exch_kernel<false, 4>);
+        QF_CUDA_TRY(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, SLAB_THREADS, smem));
+        if ((long long)per_sm * ctx->sm_count < (long long)grid.x)
+            return fail(ctx, QF_ERR_UNSUPPORTED,
+                        "an exchanging launch of " + std::to_string(grid.x) + " thread blocks is not resident at once (" +
+                            std::to_string(per_sm) + " per SM fit)");
+        if (bf)
+            le = mt == 1   ? launch_kernel(gemv_slab_exch_kernel<true, 1>, grid, blk, smem, s, pdl, p, *ar)
+                 : mt == 2 ? launch_kernel(gemv_slab_exch_kernel<true, 2>, grid, blk, smem, s, pdl, p, *ar)
+                           : launch_kernel(gemv_slab_exch_kernel<true, 4>, grid, blk, smem, s, pdl, p, *ar);
+        else
+            le = mt == 1   ? launch_kernel(gemv_slab_exch_kernel<false, 1>, grid, blk, smem, s, pdl, p, *ar)
+                 : mt == 2 ? launch_kernel(gemv_slab_exch_kernel<false, 2>, grid, blk, smem, s, pdl, p, *ar)
+                           : launch_kernel(gemv_slab_exch_kernel<false, 4>, grid, blk, smem, s, pdl, p, *ar);
+    } else if (bf) {
         le = mt == 1   ? launch_kernel(gemv_slab_kernel<true, 1>, grid, blk, smem, s, pdl, p)
              : mt == 2 ? launch_kernel(gemv_slab_kernel<true, 2>, grid, blk, smem, s, pdl, p)
                        : launch_kernel(gemv_slab_kernel<true, 4>, grid, blk, smem, s, pdl, p);
@@ -589,6 +758,16 @@ int launch_gemv_slab(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, con
     QF_CUDA_TRY(ctx, le);
     QF_CUDA_TRY(ctx, cudaGetLastError());
     return QF_OK;
+}
+
+int launch_gemv_slab(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *blob, void *Y,
+                     const void *residual, void *ws, cudaStream_t s) {
+    return launch_gemv_slab_impl(ctx, d, plan, X, blob, Y, residual, ws, s, nullptr);
+}
+
+int launch_gemv_slab_ar(qf_ctx *ctx, const qf_linear_desc *d, const Plan &plan, const void *X, const void *blob,
+                        void *Y, void *ws, cudaStream_t s, const ArParams &ar) {
+    return launch_gemv_slab_impl(ctx, d, plan, X, blob, Y, nullptr, ws, s, &ar);
 }
 
 }  // namespace qf

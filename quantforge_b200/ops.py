@@ -377,28 +377,44 @@ class Comm:
 
 def _linear_exchange(fn_name, gather, x, qweight, scales, zeros, comm, group_size, zero_const, out_dtype, path,
                      split_k, out, weight_layout):
-    dev = _need_cuda(x, qweight, scales, zeros)
-    M, N, K = _check_linear_tensors(x, qweight, scales, zeros, group_size)
-    out_dtype = out_dtype or x.dtype
-    x, qweight, scales = x.contiguous(), qweight.contiguous(), scales.contiguous()
-    zeros = zeros.contiguous() if zeros is not None else None
+    if isinstance(qweight, SlabWeight):
+        w = qweight
+        dev = _need_cuda(x, w.blob)
+        if x.dim() != 2 or x.shape[1] != w.K or x.dtype != w.act_dtype:
+            raise ValueError(f"x must be [M, {w.K}] of the dtype the slab was built for")
+        M, N, K = x.shape[0], w.N, w.K
+        x = x.contiguous()
+        d = LinearDesc()
+        d.M, d.N, d.K, d.group_size = M, N, K, w.group_size
+        d.act_dtype, d.zero_mode, d.zero_const = _DT[x.dtype], w.zero_mode, w.zero_const
+        d.path, d.split_k, d.weight_layout = QF_PATH_AUTO, split_k, QF_LAYOUT_GEMV_SLAB
+        out_dtype = out_dtype or x.dtype
+        d.out_dtype = _DT[out_dtype]
+        ptr_w, ptr_s, ptr_z = _ptr(w.blob), _ptr(None), _ptr(None)
+    else:
+        dev = _need_cuda(x, qweight, scales, zeros)
+        M, N, K = _check_linear_tensors(x, qweight, scales, zeros, group_size)
+        out_dtype = out_dtype or x.dtype
+        x, qweight, scales = x.contiguous(), qweight.contiguous(), scales.contiguous()
+        zeros = zeros.contiguous() if zeros is not None else None
+        d = _make_desc(M, N, K, group_size, x.dtype, out_dtype, zeros, zero_const, path, split_k, weight_layout)
+        ptr_w, ptr_s, ptr_z = _ptr(qweight), _ptr(scales), _ptr(zeros)
     shape = (M, N * comm.world) if gather else (M, N)
     if out is None:
         out = torch.empty(shape, dtype=out_dtype, device=dev)
     elif tuple(out.shape) != shape or out.dtype != out_dtype or not out.is_contiguous():
         raise ValueError(f"out must be a contiguous {list(shape)} tensor of out_dtype")
-    d = _make_desc(M, N, K, group_size, x.dtype, out_dtype, zeros, zero_const, path, split_k, weight_layout)
     ctx = _ctx(dev)
     with torch.cuda.device(dev):
         ws = _workspace(dev, workspace_bytes(d))
-        st = getattr(_lib.load(), fn_name)(ctx, comm._h, ctypes.byref(d), _ptr(x), _ptr(qweight), _ptr(scales),
-                                           _ptr(zeros), _ptr(out), _ptr(ws), ws.numel() if ws is not None else 0,
+        st = getattr(_lib.load(), fn_name)(ctx, comm._h, ctypes.byref(d), _ptr(x), ptr_w, ptr_s, ptr_z,
+                                           _ptr(out), _ptr(ws), ws.numel() if ws is not None else 0,
                                            _stream(dev))
     _check(st, ctx)
     return out
 
 
-def w4a16_linear_allreduce(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
+def w4a16_linear_allreduce(x: torch.Tensor, qweight, scales: Optional[torch.Tensor],
                            zeros: Optional[torch.Tensor], comm: Comm, group_size: int = 128, zero_const: int = 8,
                            out_dtype: Optional[torch.dtype] = None, split_k: int = 0,
                            out: Optional[torch.Tensor] = None, path: int = QF_PATH_AUTO,
@@ -409,7 +425,7 @@ def w4a16_linear_allreduce(x: torch.Tensor, qweight: torch.Tensor, scales: torch
                             zero_const, out_dtype, path, split_k, out, weight_layout)
 
 
-def w4a16_linear_allgather(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
+def w4a16_linear_allgather(x: torch.Tensor, qweight, scales: Optional[torch.Tensor],
                            zeros: Optional[torch.Tensor], comm: Comm, group_size: int = 128, zero_const: int = 8,
                            out_dtype: Optional[torch.dtype] = None, split_k: int = 0,
                            out: Optional[torch.Tensor] = None, path: int = QF_PATH_AUTO,

@@ -63,7 +63,7 @@ class _Linear:
         zr = ops.pack_zeros_u4(z8)
         self.slab = None
         self.layout = QF_LAYOUT_CANONICAL
-        if not exchange and batch <= QF_SLAB_MAX_M and N % 64 == 0:
+        if batch <= QF_SLAB_MAX_M and N % 64 == 0:
             self.slab = ops.prepack_gemv_slab(qw, sc, zr, GROUP)
             self.qw = self.sc = self.zr = None
         else:
@@ -141,8 +141,11 @@ class DecodeLinearStack:
     def _row(self, lin: _Linear, x, out, residual=None):
         """Row-parallel linear + sum over ranks (+ the residual stream on one GPU)."""
         if self.comm is not None:
-            ops.w4a16_linear_allreduce(x, lin.qw, lin.sc, lin.zr, self.comm, group_size=GROUP, out=out,
-                                       weight_layout=lin.layout)
+            if lin.slab is not None:
+                ops.w4a16_linear_allreduce(x, lin.slab, None, None, self.comm, out=out)
+            else:
+                ops.w4a16_linear_allreduce(x, lin.qw, lin.sc, lin.zr, self.comm, group_size=GROUP, out=out,
+                                           weight_layout=lin.layout)
             return
         if residual is not None:
             lin(x, out, QF_EPI_RESIDUAL_ADD, residual)
@@ -161,8 +164,6 @@ class DecodeLinearStack:
         b = self.buf
         if self.fuse:
             ly["qkv"](h, b["qkv"])
-            if self.residual:
-                b["o"].copy_(h) if False else None
             self._row(ly["o"], b["attn"], b["o"], h if self.residual else None)
             if self.epilogues:
                 ly["gate_up"](b["o"], b["act"], QF_EPI_SILU_MUL)

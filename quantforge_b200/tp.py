@@ -69,7 +69,10 @@ class ColumnParallelLinear:
 
     def __init__(self, qweight, scales, zeros=None, group_size: int = 128, zero_const: int = 8,
                  group: Optional[dist.ProcessGroup] = None, gather_output: bool = True,
-                 compute: Optional[Callable] = None, prepack: bool = False, comm: Optional["ops.Comm"] = None):
+                 compute: Optional[Callable] = None, prepack: bool = False, comm: Optional["ops.Comm"] = None,
+                 slab: bool = False):
+        """slab=True additionally prepacks the shard for the streaming GEMV kernel, which then serves batches of up
+        to 32 rows (N/world must be a multiple of 64)."""
         self.comm = comm
         self.group = group
         self.world = dist.get_world_size(group)
@@ -81,6 +84,9 @@ class ColumnParallelLinear:
         self.N = self.N_local * self.world
         self.weight_layout = ops.QF_LAYOUT_CANONICAL
         self.compute = compute
+        self.slab = None
+        if compute is None and slab:
+            self.slab = ops.prepack_gemv_slab(self.qweight, self.scales, self.zeros, group_size, zero_const)
         if compute is None and prepack and self.N_local % 128 == 0:
             self.qweight = ops.prepack_w4(self.qweight)
             self.weight_layout = ops.QF_LAYOUT_INTERLEAVED
@@ -88,12 +94,16 @@ class ColumnParallelLinear:
     def _local(self, x, out_dtype):
         if self.compute is not None:
             return self.compute(x, self.qweight, self.scales, self.zeros, self.group_size, self.zero_const, out_dtype)
+        if self.slab is not None and x.shape[0] <= ops.QF_SLAB_MAX_M:
+            return ops.w4a16_linear(x, self.slab, out_dtype=out_dtype)
         return ops.w4a16_linear(x, self.qweight, self.scales, self.zeros, self.group_size, self.zero_const, out_dtype,
                                 weight_layout=self.weight_layout)
 
     def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         if (self.comm is not None and self.compute is None and self.gather_output and self.world > 1 and
                 x.shape[0] <= 64):
+            if self.slab is not None and x.shape[0] <= ops.QF_SLAB_MAX_M:
+                return ops.w4a16_linear_allgather(x, self.slab, None, None, self.comm, out_dtype=out_dtype)
             return ops.w4a16_linear_allgather(x, self.qweight, self.scales, self.zeros, self.comm, self.group_size,
                                               self.zero_const, out_dtype, weight_layout=self.weight_layout)
         y = self._local(x, out_dtype)
@@ -116,7 +126,9 @@ class RowParallelLinear:
     def __init__(self, qweight, scales, zeros=None, group_size: int = 128, zero_const: int = 8,
                  group: Optional[dist.ProcessGroup] = None, input_is_parallel: bool = True,
                  reduce_dtype: torch.dtype = torch.float32, compute: Optional[Callable] = None,
-                 prepack: bool = False, comm: Optional["ops.Comm"] = None):
+                 prepack: bool = False, comm: Optional["ops.Comm"] = None, slab: bool = False):
+        """slab=True additionally prepacks the shard for the streaming GEMV kernel (batches of up to 32 rows; N must
+        be a multiple of 64)."""
         self.comm = comm
         self.group = group
         self.world = dist.get_world_size(group)
@@ -128,6 +140,9 @@ class RowParallelLinear:
         self.K_local = self.qweight.shape[1] * _codes_per_elem(self.qweight)
         self.weight_layout = ops.QF_LAYOUT_CANONICAL
         self.compute = compute
+        self.slab = None
+        if compute is None and slab:
+            self.slab = ops.prepack_gemv_slab(self.qweight, self.scales, self.zeros, group_size, zero_const)
         if compute is None and prepack and self.qweight.shape[0] % 128 == 0:
             self.qweight = ops.prepack_w4(self.qweight)
             self.weight_layout = ops.QF_LAYOUT_INTERLEAVED
@@ -136,12 +151,17 @@ class RowParallelLinear:
         out_dtype = out_dtype or x.dtype
         if not self.input_is_parallel:
             x = x[:, self.rank * self.K_local:(self.rank + 1) * self.K_local].contiguous()
+        use_slab = self.slab is not None and x.shape[0] <= ops.QF_SLAB_MAX_M
         if self.comm is not None and self.compute is None and x.shape[0] <= 64:
+            if use_slab:
+                return ops.w4a16_linear_allreduce(x, self.slab, None, None, self.comm, out_dtype=out_dtype)
             return ops.w4a16_linear_allreduce(x, self.qweight, self.scales, self.zeros, self.comm, self.group_size,
                                               self.zero_const, out_dtype, weight_layout=self.weight_layout)
         if self.compute is not None:
             y = self.compute(x, self.qweight, self.scales, self.zeros, self.group_size, self.zero_const,
                              self.reduce_dtype)
+        elif use_slab:
+            y = ops.w4a16_linear(x, self.slab, out_dtype=self.reduce_dtype)
         else:
             y = ops.w4a16_linear(x, self.qweight, self.scales, self.zeros, self.group_size, self.zero_const,
                                  self.reduce_dtype, weight_layout=self.weight_layout)

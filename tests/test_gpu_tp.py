@@ -60,19 +60,25 @@ def _worker(rank, world, port, out):
         dist.destroy_process_group()
 
 
-def test_column_then_row_parallel_on_two_gpus():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("world", [2, 4])
+def test_column_then_row_parallel(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     out = ctx.SimpleQueue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, out)) for r in range(world)]
     for p in procs:
         p.start()
+    codes = []
     for p in procs:
         p.join(300)
-        assert p.exitcode == 0
+        if p.is_alive():
+            p.terminate()
+            p.join(30)
+        codes.append(p.exitcode)
+    assert codes == [0] * world
     errs = out.get()
     assert errs[0] < 1e-4 and errs[2] < 1e-4          # all-gathered column-parallel output, fp32
     assert errs[1] < 1e-2 and errs[3] < 1e-2          # bf16 intermediate between the two linears
