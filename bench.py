@@ -275,7 +275,7 @@ def time_case(env, M, K, N, act, out_dt, sym, sigma, slab, copies=None, reps=5, 
     wbytes = K * N // 2
     n = copies or max(3, -(-300_000_000 // wbytes))
     G = K // GROUP
-    use_slab = slab and M <= 32 and N % 64 == 0
+    use_slab = slab and M <= 8 and N % 64 == 0
     layout = LAYOUT_INTERLEAVED if ((M > 2 or N * K // 2 >= (32 << 20)) and N % 128 == 0) else LAYOUT_CANONICAL
     sets = []
     for _ in range(n):
@@ -351,7 +351,7 @@ def single_gpu_extras(env, args):
             us = time_case(env, M, K, N, torch.bfloat16, torch.bfloat16, False, 0.02, True, gen=gen)
             b = algo_bytes(M, K, N)
             detail.append({"M": M, "K": K, "N": N, "us": round(us, 2), "gbs": round(b / us / 1e3, 1),
-                           "frac_hbm": round(b / us / 1e3 / hbm, 3), "kernel": "gemv_slab" if M <= 32 else "gemm_tcgen05"})
+                           "frac_hbm": round(b / us / 1e3 / hbm, 3), "kernel": "gemv_slab" if M <= 8 else "gemm_tcgen05"})
     b = algo_bytes(1, 4096, 4096)
     us = time_case(env, 1, 4096, 4096, torch.float16, torch.float16, False, 0.02, True, gen=gen)
     us_old = time_case(env, 1, 4096, 4096, torch.float16, torch.float16, False, 0.02, False, gen=gen)
@@ -454,7 +454,8 @@ def run_stack_workload(env, args):
     fuse = not args.no_fuse
     in_kernel = world > 1 and not args.nccl_collectives and args.batch <= 64
     st = S.DecodeLinearStack(cfg, args.batch, torch.bfloat16, dev, world, rank, None, args.layers or None,
-                             fuse=fuse, fused_allreduce=in_kernel, epilogues=args.epilogues)
+                             fuse=fuse, fused_allreduce=in_kernel, epilogues=args.epilogues,
+                             exchange_in_slab_kernel=not args.legacy_exchange_kernels)
     # ---- parity before anything is timed: layer 0, every linear, sampled columns, against the CPU oracle ----
     parity = st.check_parity(oracle_linear, oracle_silu_mul)
     parity["tolerance"] = 1e-2
@@ -532,8 +533,8 @@ def run_stack_workload(env, args):
     if rank == 0:
         gbs = nbytes / (ms * 1e-3) / 1e9
         per_launch_us = ms * 1e3 / launches_per_step
-        kernel = "qf::gemv_slab_kernel" if args.batch <= 32 else "qf::gemm_kernel (tcgen05)"
-        if in_kernel and args.batch <= 32:
+        kernel = "qf::gemv_slab_kernel" if args.batch <= 8 else "qf::gemm_kernel (tcgen05)"
+        if in_kernel and args.batch <= 8:
             kernel += " + qf::gemv_slab_exch_kernel (row-parallel linears)"
         line = {
             "metric": "w4a16_linear_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -598,7 +599,7 @@ def run_sweep_workload(env, args):
             zr = qf.pack_zeros_u4(torch.randint(0, 16, (G, Nl), dtype=torch.int8, device=dev, generator=gen))
             slab = None
             layout = LAYOUT_CANONICAL
-            if M <= 32 and Nl % 64 == 0:
+            if M <= 8 and Nl % 64 == 0:
                 slab = qf.prepack_gemv_slab(qw, sc, zr, GROUP)
             elif Nl % 128 == 0:
                 qw = qf.prepack_w4(qw, layout=LAYOUT_INTERLEAVED)
@@ -660,7 +661,7 @@ def run_sweep_workload(env, args):
                         if comm is not None else f"column-parallel x{world} + NCCL all-gather"),
                        "l2": "inputs larger than L2: 15 weight copies, 335 MB touched per step",
                        "timed_region_s": sum(per_bracket) * 1e-3},
-            "roofline": {"bound": "hbm", "kernel": "whole step (slab GEMV for M <= 16, tcgen05 for M = 64)",
+            "roofline": {"bound": "hbm", "kernel": "whole step (slab GEMV for M <= 8, tcgen05 for M = 16, 64)",
                          "achieved": gbs / world, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / world / pk["hbm_gbs"],
                          "traffic": None, "peak_source": pk["source"]},
             "cpu_baseline": None, "e2e": None, "gpu_launches": len(cases) * args.steps, "clocks": clocks,
@@ -686,6 +687,8 @@ def main():
                     help="stack workloads: SiLU*mul inside gate/up and (one GPU) the residual adds inside o / down")
     ap.add_argument("--nccl-collectives", action="store_true",
                     help="N > 1 GPUs: follow each linear with an NCCL collective instead of exchanging in-kernel")
+    ap.add_argument("--legacy-exchange-kernels", action="store_true",
+                    help="N > 1: row-parallel linears exchange inside the canonical-weight kernels, not the slab kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()

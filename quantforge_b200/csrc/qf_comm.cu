@@ -185,8 +185,11 @@ static int linear_exchange(qf_ctx *ctx, qf_comm *comm, const qf_linear_desc *des
     qf_linear_desc local_desc = *desc;
     if (local_desc.weight_layout == QF_LAYOUT_GEMV_SLAB && local_desc.split_k == 0) {
         // A collecting thread block waits for its peers while it holds its SM slot, so every thread block of the
-        // launch must be resident at once on every rank: two per SM always fit (registers, shared memory).
-        local_desc.split_k = 2 * ctx->sm_count;
+        // launch must be resident at once on every rank: an explicit grid of whole multiples of the SM count (the
+        // launch checks it against the occupancy the kernel really gets). Same size rule as the plain kernel.
+        const long long wbytes = (long long)(local_desc.N / 64) * (local_desc.K / 128) * QF_SLAB_UNIT_BYTES;
+        const int per_sm = (wbytes <= (16ll << 20)) ? 2 : (local_desc.M > 16 ? 3 : 4);
+        local_desc.split_k = per_sm * ctx->sm_count;
         desc = &local_desc;
     }
     Plan plan;

@@ -29,6 +29,7 @@
 // which were dispatched before it.
 #include <algorithm>
 #include <cstdlib>
+#include <type_traits>
 
 #include "qf_common.cuh"
 #include "qf_mbar.cuh"
@@ -59,9 +60,19 @@ struct SlabParams {
     int epilogue;
 };
 
-__device__ __forceinline__ uint32_t lds32g(uint32_t addr) {
+// Shared-memory loads with the constant part of the address as an immediate (no address arithmetic in the loop).
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32_at(uint32_t base) {
     uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(base), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint4 lds128_at(uint32_t base) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(base), "n"(OFF));
     return v;
 }
 // Two (value, token) words with one 16-byte access; each 8-byte word is written and read whole.
@@ -335,24 +346,32 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
             aborted = true;
             break;
         }
-        const uint4 va = lds128g(wptr);
-        const uint4 vb = lds128g(wptr + 512u);
-        const ZeroScale<BF16> za = slab_consts<BF16>(lds32g(wptr + cst_off));
-        const ZeroScale<BF16> zb = slab_consts<BF16>(lds32g(wptr + cst_off + 32u));
+        const uint4 va = lds128_at<0>(wptr);
+        const uint4 vb = lds128_at<512>(wptr);
+        const uint32_t cptr = wptr + cst_off;
+        const ZeroScale<BF16> za = slab_consts<BF16>(lds32_at<0>(cptr));
+        const ZeroScale<BF16> zb = slab_consts<BF16>(lds32_at<32>(cptr));
         const uint32_t wa[4] = {va.x, va.y, va.z, va.w};
         const uint32_t wb[4] = {vb.x, vb.y, vb.z, vb.w};
+        uint32_t xptr[MT];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int nt = 0; nt < MT; ++nt) xptr[nt] = wptr + x_off[nt];
+        auto step = [&](auto jc) {
+            constexpr int j = decltype(jc)::value;
             uint32_t pa[4], pb[4];
             dequant8<BF16>(wa[j], za, pa);
             dequant8<BF16>(wb[j], zb, pb);
 #pragma unroll
             for (int nt = 0; nt < MT; ++nt) {
-                const uint4 xb = lds128g(wptr + x_off[nt] + (uint32_t)j * 64u);
+                const uint4 xb = lds128_at<j * 64>(xptr[nt]);
                 mma_16816<BF16>(acc[nt][0], pa[0], pb[0], pa[1], pb[1], xb.x, xb.y);
                 mma_16816<BF16>(acc[nt][1], pa[2], pb[2], pa[3], pb[3], xb.z, xb.w);
             }
-        }
+        };
+        step(std::integral_constant<int, 0>{});
+        step(std::integral_constant<int, 1>{});
+        step(std::integral_constant<int, 2>{});
+        step(std::integral_constant<int, 3>{});
         __syncwarp();
         if (lane == 0) mbar_arrive(ebar);
         if (++s == p.depth) {
@@ -497,11 +516,12 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
 }
 
 template <bool BF16, int MT>
-__global__ void __launch_bounds__(SLAB_THREADS) gemv_slab_kernel(const SlabParams p) {
+__global__ void __launch_bounds__(SLAB_THREADS, MT <= 2 ? 4 : 3) gemv_slab_kernel(const SlabParams p) {
     gemv_slab_body<BF16, MT, false>(p, NoExchange{});
 }
 template <bool BF16, int MT>
-__global__ void __launch_bounds__(SLAB_THREADS) gemv_slab_exch_kernel(const SlabParams p, const ArParams ar) {
+__global__ void __launch_bounds__(SLAB_THREADS, MT <= 2 ? 4 : 3)
+gemv_slab_exch_kernel(const SlabParams p, const ArParams ar) {
     gemv_slab_body<BF16, MT, true>(p, ar);
 }
 
@@ -643,15 +663,15 @@ void slab_geometry(int64_t M, int64_t N, int64_t K, int sm_count, int grid_reque
     const long long units = (N / 64) * (K / 128);
     const int m_pad = slab_m_pad(M);
     const size_t stage = SLAB_UNIT_BYTES + (size_t)m_pad * SLAB_X_PITCH;
-    int ctas = 1;
-    for (int cand = 4; cand >= 1; --cand) {
-        const long long per = units / ((long long)sm_count * cand);
-        const long long fit = (long long)((200u << 10) / cand / stage);
-        if ((per >= 4 && fit >= 6) || cand == 1) {
-            ctas = cand;
-            break;
-        }
-    }
+    // Measured on B200 (M = 1, bf16, CUDA-graph replays on weights that are not in L2; us per launch):
+    //   8.4 MB:  2 blocks/SM 5.7-5.8, 3: 6.8-7.0, 4: 7.3-7.4      30 MB: 2: 12.1-14.7, 3: 12.5-13.3, 4: 11.5-12.3
+    //   42 MB:   2: 15.9-19.7, 4: 14.8-15.2                        235 MB: 1: 114, 2: 76-92, 3: 68-79, 4: 65.5
+    // Large matrices want every warp slot streaming; small ones want room left on the SM, so that the next kernel of
+    // the stream (programmatic dependent launch) is resident with its weights already in flight when this one ends.
+    const long long wbytes = units * SLAB_UNIT_BYTES;
+    int ctas = wbytes <= (16ll << 20) ? 2 : 4;
+    if (m_pad > 16) ctas = std::min(ctas, 3);  // register budget of the four-batch-tile instantiation
+    while (ctas > 1 && units / ((long long)sm_count * ctas) < 2) --ctas;
     if (env_ctas > 0) ctas = env_ctas;
     long long grid = (long long)sm_count * ctas;
     if (grid_request > 0) {
@@ -665,6 +685,7 @@ void slab_geometry(int64_t M, int64_t N, int64_t K, int sm_count, int grid_reque
     const long long per_max = (units + grid - 1) / grid;
     if (depth > per_max) depth = per_max;
     if (depth > SLAB_MAX_DEPTH) depth = SLAB_MAX_DEPTH;
+    if (depth > 6) depth = 6;  // deeper rings measured equal or slower; shallow ones leave room on the SM
     if (env_depth > 0) depth = env_depth;
     if (depth < 1) depth = 1;
     while (depth > 1 && slab_smem_bytes((int)depth, m_pad) > (size_t)(220u << 10)) --depth;

@@ -13,7 +13,7 @@ Modes
                    on one GPU o and down add the residual stream in their epilogue
   fused_allreduce  (world > 1, batch <= 64) the row-parallel o and down linears sum across ranks inside the kernel
                    over NVLink peer memory instead of being followed by an NCCL all-reduce
-Batches of up to 32 rows read QF_LAYOUT_GEMV_SLAB weights (the streaming GEMV kernel), larger ones the
+Batches of up to 8 rows read QF_LAYOUT_GEMV_SLAB weights (the streaming GEMV kernel), larger ones the
 interleaved layout of the tcgen05 kernel.
 """
 from __future__ import annotations
@@ -24,12 +24,12 @@ import torch
 import torch.distributed as dist
 
 from . import ops
-from ._lib import (QF_EPI_NONE, QF_EPI_RESIDUAL_ADD, QF_EPI_SILU_MUL, QF_LAYOUT_CANONICAL, QF_LAYOUT_INTERLEAVED,
-                   QF_SLAB_MAX_M)
+from ._lib import QF_EPI_NONE, QF_EPI_RESIDUAL_ADD, QF_EPI_SILU_MUL, QF_LAYOUT_CANONICAL, QF_LAYOUT_INTERLEAVED
 
 LLAMA3_8B = {"hidden": 4096, "kv": 1024, "ffn": 14336, "layers": 32}
 LLAMA3_70B = {"hidden": 8192, "kv": 1024, "ffn": 28672, "layers": 80}
 GROUP = 128
+SLAB_BATCH = 8  # up to here the streaming GEMV kernel is the faster one (measured); beyond, the tcgen05 kernel
 SAMPLE_COLUMNS = 64  # output columns per linear of layer 0 kept on the CPU for `check_parity`
 
 
@@ -63,7 +63,7 @@ class _Linear:
         zr = ops.pack_zeros_u4(z8)
         self.slab = None
         self.layout = QF_LAYOUT_CANONICAL
-        if batch <= QF_SLAB_MAX_M and N % 64 == 0:
+        if batch <= SLAB_BATCH and N % 64 == 0 and not exchange:
             self.slab = ops.prepack_gemv_slab(qw, sc, zr, GROUP)
             self.qw = self.sc = self.zr = None
         else:
@@ -75,15 +75,18 @@ class _Linear:
 
     def __call__(self, x, out, epilogue=QF_EPI_NONE, residual=None):
         if self.slab is not None:
-            return ops.w4a16_linear(x, self.slab, out=out, epilogue=epilogue, residual=residual)
-        return ops.w4a16_linear(x, self.qw, self.sc, self.zr, group_size=GROUP, out=out, weight_layout=self.layout,
-                                epilogue=epilogue, residual=residual)
+            return ops.w4a16_linear(x, self.slab, out=out, out_dtype=out.dtype, epilogue=epilogue, residual=residual)
+        return ops.w4a16_linear(x, self.qw, self.sc, self.zr, group_size=GROUP, out=out, out_dtype=out.dtype,
+                                weight_layout=self.layout, epilogue=epilogue, residual=residual)
 
 
 class DecodeLinearStack:
     def __init__(self, cfg: dict, batch: int, dtype=torch.bfloat16, device=None, world: int = 1, rank: int = 0,
                  group: Optional[dist.ProcessGroup] = None, layers: Optional[int] = None, seed: int = 0,
-                 fuse: bool = False, fused_allreduce: bool = False, epilogues: bool = False):
+                 fuse: bool = False, fused_allreduce: bool = False, epilogues: bool = False,
+                 exchange_in_slab_kernel: bool = True):
+        """exchange_in_slab_kernel=False keeps the row-parallel linears of a fused_allreduce stack on the kernels
+        that read canonical / interleaved weights (their last-arriving thread block exchanges each tile)."""
         self.cfg, self.M, self.dtype = cfg, batch, dtype
         self.dev = device or torch.device("cuda", torch.cuda.current_device())
         self.world, self.rank, self.group = world, rank, group
@@ -101,7 +104,7 @@ class DecodeLinearStack:
             if batch > 64:
                 raise ValueError("fused_allreduce needs batch <= 64")
             self.comm = ops.Comm(batch * H, device=self.dev, group=group)
-        exch = self.comm is not None
+        exch = self.comm is not None and not exchange_in_slab_kernel
         self.layers = []
         for li in range(self.L):
             s = li == 0
@@ -142,17 +145,17 @@ class DecodeLinearStack:
         """Row-parallel linear + sum over ranks (+ the residual stream on one GPU)."""
         if self.comm is not None:
             if lin.slab is not None:
-                ops.w4a16_linear_allreduce(x, lin.slab, None, None, self.comm, out=out)
+                ops.w4a16_linear_allreduce(x, lin.slab, None, None, self.comm, out=out, out_dtype=out.dtype)
             else:
                 ops.w4a16_linear_allreduce(x, lin.qw, lin.sc, lin.zr, self.comm, group_size=GROUP, out=out,
-                                           weight_layout=lin.layout)
+                                           out_dtype=out.dtype, weight_layout=lin.layout)
             return
         if residual is not None:
             lin(x, out, QF_EPI_RESIDUAL_ADD, residual)
         else:
             lin(x, out)
         if self.world > 1:
-            dist.all_reduce(out, group=self.group)
+            dist.all_reduce(out, group=self.group)  # in the output's type (bf16 in the timed step, fp32 in the check)
 
     def close(self):
         self._graph = None
@@ -230,6 +233,8 @@ class DecodeLinearStack:
         with `oracle_linear(x, qweight_rows, scales, zeros, group) -> float array [M, rows]` (a CPU restatement the
         caller provides; this package has none). Row-parallel linears are compared after the sum over ranks, with
         the oracle's partial sums added across ranks in float64; every rank must also hold identical bits.
+        The comparison is made on fp32 outputs of the same kernels (rounding an exact result to bf16 alone costs up
+        to 1.3e-2 of the output's rms on layers this wide, more than the tolerance the path is specified with).
         Returns {"max_rel_err", "cases", "ranks_bit_identical"}; errors are max |y - ref| / rms(ref)."""
         import numpy as np
         b = self.buf
@@ -245,9 +250,14 @@ class DecodeLinearStack:
             rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
             return float(np.max(np.abs(y_cols.astype(np.float64) - ref)) / max(rms, 1e-30))
 
-        def column(lin, x, out, epilogue=QF_EPI_NONE):
+        def f32(t):
+            return torch.empty(t.shape, dtype=torch.float32, device=t.device)
+
+        def column(lin, x, buf, epilogue=QF_EPI_NONE):
             nonlocal worst, cases
+            out = f32(buf)
             lin(x, out, epilogue)
+            buf.copy_(out)  # the next linear of the layer reads it
             torch.cuda.synchronize()
             ref = ref_of(lin, x)
             if lin.silu:
@@ -257,9 +267,11 @@ class DecodeLinearStack:
             worst = max(worst, err_of(y, ref))
             cases += 1
 
-        def row(lin, x, out):
+        def row(lin, x, buf):
             nonlocal worst, cases, identical
+            out = f32(buf)
             self._row(lin, x, out)
+            buf.copy_(out)
             torch.cuda.synchronize()
             part = torch.from_numpy(np.ascontiguousarray(ref_of(lin, x), dtype=np.float64)).to(self.dev)
             if self.world > 1:
