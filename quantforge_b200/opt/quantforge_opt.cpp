@@ -16,8 +16,11 @@
 //                                   func.call @qf_w4a16_linear, a lone qf.unpack by @qf_unpack_int4 and a lone
 //                                   qf.dequant(qf.unpack) by @qf_dequant_w4 (entry points of quantforge_rt.h).
 // Exit code 0 on success, 1 on failure (diagnostics on stderr), as MlirOptMain's asMainReturnCode.
-// The reference's other passes (lower-unpack-to-*, the generic GPU scaffolding) are not part of this
-// build: asking for them is an error, there is nothing to fall back to.
+//   --lower-unpack-to-arith / --lower-unpack-branch-free / --lower-unpack-to-nvvm / --lower-unpack-to-prmt,
+//   --lower-dequant-to-arith, --fuse-unpack-dequant-branch-free: the reference's scalar lowerings
+//                                   (lib/Transforms/LowerUnpack*.cpp, LowerDequantToArith.cpp), emitted as text
+// The reference's generic GPU scaffolding passes (tiling .. lower-to-nvvm) and register-layout-aware-unpack are
+// not part of this build: asking for them is an error.
 //
 // The IR model is deliberately small: a module is a list of top-level chunks; a function is a header,
 // a list of statements and a closing brace; a statement is the text of one operation (possibly spanning
@@ -56,6 +59,15 @@ struct Chunk {
 struct Module {
     std::vector<Chunk> chunks;
     std::set<std::string> runtime_decls;  // private declarations to append
+    std::vector<std::pair<std::string, std::string>> aliases;  // (#name, affine_map<...>) printed at the top
+    // Attribute alias for an affine map, created on first use (#map, #map1, ...), as the MLIR printer hoists them.
+    std::string alias(const std::string &map) {
+        for (const auto &a : aliases)
+            if (a.second == map) return a.first;
+        const std::string name = aliases.empty() ? "#map" : "#map" + std::to_string(aliases.size());
+        aliases.emplace_back(name, map);
+        return name;
+    }
 };
 
 [[noreturn]] void die(const std::string &msg) {
@@ -199,6 +211,7 @@ Module parse(std::istream &in) {
 }
 
 void print(const Module &mod, std::ostream &os) {
+    for (const auto &a : mod.aliases) os << a.first << " = " << a.second << "\n";
     bool wrote_decls = mod.runtime_decls.empty();
     for (const auto &c : mod.chunks) {
         if (!c.is_func) {
@@ -429,9 +442,16 @@ void pass_convert(Module &mod, int bitwidth) {
             const TensorTy w_i8 = m.rhs_ty;
             const TensorTy w_f16 = m.rhs_ty.with_elem("f16");
             const std::string u = fresh("unpack"), sc = fresh("scale"), z = fresh("zp"), dq = fresh("dequant");
-            out.push_back(mk(ind + u + " = qf.unpack " + m.rhs + " : " + w_i8.str() + " -> " + w_i8.str()));
+            // Where the weight itself is a constant of the function, MLIR's folder keeps the new constants with it,
+            // ahead of the unpack (the order the reference's tests with attribute-carrying constants expect).
+            const Stmt *wdef = find_def(f, m.rhs);
+            const bool consts_first = wdef && wdef->op == "arith.constant";
+            if (!consts_first)
+                out.push_back(mk(ind + u + " = qf.unpack " + m.rhs + " : " + w_i8.str() + " -> " + w_i8.str()));
             out.push_back(mk(ind + sc + " = arith.constant " + scale + " : tensor<f16>"));
             out.push_back(mk(ind + z + " = arith.constant " + zp + " : tensor<i8>"));
+            if (consts_first)
+                out.push_back(mk(ind + u + " = qf.unpack " + m.rhs + " : " + w_i8.str() + " -> " + w_i8.str()));
             out.push_back(mk(ind + dq + " = qf.dequant " + u + ", " + sc + ", " + z + " : " + w_i8.str() +
                              ", tensor<f16>, tensor<i8> -> " + w_f16.str()));
             std::string lhs = m.lhs;
@@ -747,9 +767,318 @@ void pass_lower_to_runtime(Module &mod) {
     }
 }
 
+
+// ---- the reference's scalar lowerings of qf.unpack / qf.dequant ----------------------------------------
+// They define the arithmetic the runtime kernels implement (and the CPU oracle restates); emitting them keeps the
+// driver usable for inspecting that arithmetic and keeps every reference flag of the hot path alive.
+
+// [.., n] -> [.., 2n] with every leading extent equal
+bool unpack_doubles(const Unpack &u) {
+    const size_t r = u.in_ty.dims.size();
+    if (r < 1 || u.out_ty.dims.size() != r) return false;
+    for (size_t k = 0; k + 1 < r; ++k)
+        if (u.in_ty.dims[k] != u.out_ty.dims[k]) return false;
+    for (const auto &d : u.in_ty.dims)
+        if (d == "?") return false;
+    return std::to_string(2 * std::stoll(u.in_ty.dims[r - 1])) == u.out_ty.dims[r - 1];
+}
+
+std::string dim_list(size_t n) {
+    std::string d;
+    for (size_t k = 0; k < n; ++k) d += (k ? ", d" : "d") + std::to_string(k);
+    return d;
+}
+
+// --lower-unpack-to-arith (lib/Transforms/LowerUnpackToArith.cpp:73-219): one generic over [.., n, 2] that selects
+// the low or the high nibble by the innermost index, then a collapse to [.., 2n].
+void pass_lower_unpack_to_arith(Module &mod) {
+    for (auto &c : mod.chunks) {
+        if (!c.is_func) continue;
+        Func &f = c.func;
+        std::vector<Stmt> out;
+        for (const Stmt &s : f.body) {
+            Unpack u;
+            if (s.op == "qf.unpack") u = parse_unpack(s);
+            if (!u.ok || u.in_ty.elem != "i8" || !unpack_doubles(u)) {
+                out.push_back(s);
+                continue;
+            }
+            const size_t r = u.in_ty.dims.size();
+            const std::string ind = indent_of(s.text);
+            TensorTy wide = u.in_ty;
+            wide.dims.push_back("2");
+            const std::string in_map = mod.alias("affine_map<(" + dim_list(r + 1) + ") -> (" + dim_list(r) + ")>");
+            const std::string out_map = mod.alias("affine_map<(" + dim_list(r + 1) + ") -> (" + dim_list(r + 1) + ")>");
+            const std::string c15 = fresh("c15"), c4 = fresh("c4"), c0 = fresh("c0"), e = fresh("empty"), gen = fresh("unpacked");
+            out.push_back(mk(ind + c15 + " = arith.constant 15 : i8"));
+            out.push_back(mk(ind + c4 + " = arith.constant 4 : i8"));
+            out.push_back(mk(ind + c0 + " = arith.constant 0 : index"));
+            out.push_back(mk(ind + e + " = tensor.empty() : " + wide.str()));
+            std::string t = ind + gen + " = linalg.generic {indexing_maps = [" + in_map + ", " + out_map +
+                            "], iterator_types = " + iter_types(r + 1) + "} ins(" + u.in + " : " + u.in_ty.str() +
+                            ") outs(" + e + " : " + wide.str() + ") {\n";
+            t += ind + "^bb0(%in: i8, %out: i8):\n";
+            t += ind + "  %lo = arith.andi %in, " + c15 + " : i8\n";
+            t += ind + "  %sh = arith.shrui %in, " + c4 + " : i8\n";
+            t += ind + "  %hi = arith.andi %sh, " + c15 + " : i8\n";
+            t += ind + "  %idx = linalg.index " + std::to_string(r) + " : index\n";
+            t += ind + "  %is_lo = arith.cmpi eq, %idx, " + c0 + " : index\n";
+            t += ind + "  %q = arith.select %is_lo, %lo, %hi : i8\n";
+            t += ind + "  linalg.yield %q : i8\n";
+            t += ind + "} -> " + wide.str();
+            out.push_back(mk(t));
+            std::string reassoc = "[";
+            for (size_t k = 0; k + 1 < r; ++k) reassoc += "[" + std::to_string(k) + "], ";
+            reassoc += "[" + std::to_string(r - 1) + ", " + std::to_string(r) + "]]";
+            out.push_back(mk(ind + s.result + " = tensor.collapse_shape " + gen + " " + reassoc + " : " + wide.str() +
+                             " into " + u.out_ty.str()));
+        }
+        f.body.swap(out);
+    }
+}
+
+// Pointwise generic over `ty` whose body is `lines` (each without indentation), yielding %r of element type `elem_out`.
+std::string pointwise_generic(const std::string &ind, const std::string &result, const std::string &ins,
+                              const std::string &ins_types, const std::string &maps, size_t rank,
+                              const std::string &out_buf, const TensorTy &out_ty, const std::string &bb_args,
+                              const std::vector<std::string> &lines) {
+    std::string t = ind + result + " = linalg.generic {indexing_maps = [" + maps + "], iterator_types = " +
+                    iter_types(rank) + "} ins(" + ins + " : " + ins_types + ") outs(" + out_buf + " : " + out_ty.str() +
+                    ") {\n";
+    t += ind + "^bb0(" + bb_args + "):\n";
+    for (const auto &l : lines) t += ind + "  " + l + "\n";
+    t += ind + "  linalg.yield %r : " + out_ty.elem + "\n";
+    t += ind + "} -> " + out_ty.str();
+    return t;
+}
+
+std::string slice_spec(const TensorTy &half, int offset_last) {
+    std::string off = "[", size = "[", stride = "[";
+    const size_t r = half.dims.size();
+    for (size_t k = 0; k < r; ++k) {
+        const bool last = k + 1 == r;
+        off += std::string(k ? ", " : "") + (last ? std::to_string(offset_last) : "0");
+        size += std::string(k ? ", " : "") + half.dims[k];
+        stride += std::string(k ? ", " : "") + (last ? "2" : "1");
+    }
+    return off + "] " + size + "] " + stride + "]";
+}
+
+// --lower-unpack-branch-free (lib/Transforms/LowerUnpackBranchFree.cpp:78-230): low and high nibbles as two
+// pointwise generics, interleaved by two stride-2 tensor.insert_slice: out[.., 2n] = low, out[.., 2n+1] = high.
+// --fuse-unpack-dequant-branch-free (lib/Transforms/FuseUnpackDequant.cpp:323-508): the same with the dequant
+// arithmetic inside both generics.
+void pass_branch_free(Module &mod, bool fuse_dequant) {
+    for (auto &c : mod.chunks) {
+        if (!c.is_func) continue;
+        Func &f = c.func;
+        std::set<std::string> dead_unpacks;
+        std::vector<Stmt> out;
+        for (const Stmt &s : f.body) {
+            Unpack u;
+            Dequant d;
+            const Stmt *def = nullptr;
+            if (!fuse_dequant && s.op == "qf.unpack") {
+                u = parse_unpack(s);
+            } else if (fuse_dequant && s.op == "qf.dequant") {
+                d = parse_dequant(s);
+                def = d.ok ? find_def(f, d.in) : nullptr;
+                if (def && def->op == "qf.unpack") u = parse_unpack(*def);
+                if (d.ok && d.out_ty.elem != "f16") u.ok = false;
+            }
+            if (!u.ok || u.in_ty.elem != "i8" || !unpack_doubles(u)) {
+                out.push_back(s);
+                continue;
+            }
+            const size_t r = u.in_ty.dims.size();
+            const std::string ind = indent_of(s.text);
+            const std::string id = identity_map(r);
+            const TensorTy half = fuse_dequant ? u.in_ty.with_elem("f16") : u.in_ty;
+            const TensorTy full = fuse_dequant ? d.out_ty : u.out_ty;
+            const std::string c15 = fresh("c15"), c4 = fresh("c4");
+            out.push_back(mk(ind + c15 + " = arith.constant 15 : i8"));
+            out.push_back(mk(ind + c4 + " = arith.constant 4 : i8"));
+            std::string halves[2];
+            for (int hi = 0; hi < 2; ++hi) {
+                const std::string e = fresh("empty"), g = fresh(hi ? "high" : "low");
+                out.push_back(mk(ind + e + " = tensor.empty() : " + half.str()));
+                std::vector<std::string> body;
+                std::string v = "%b";
+                if (hi) {
+                    body.push_back("%sh = arith.shrui %b, " + c4 + " : i8");
+                    v = "%sh";
+                }
+                if (fuse_dequant) {
+                    body.push_back("%m = arith.andi " + v + ", " + c15 + " : i8");
+                    body.push_back("%qf = arith.sitofp %m : i8 to f16");
+                    body.push_back("%zf = arith.sitofp %z : i8 to f16");
+                    body.push_back("%d = arith.subf %qf, %zf : f16");
+                    body.push_back("%r = arith.mulf %d, %s : f16");
+                    out.push_back(mk(pointwise_generic(
+                        ind, g, u.in + ", " + d.scale + ", " + d.zp, u.in_ty.str() + ", " + d.scale_ty + ", " + d.zp_ty,
+                        id + ", " + scalar_map(r) + ", " + scalar_map(r) + ", " + id, r, e, half,
+                        "%b: i8, %s: f16, %z: i8, %o: f16", body)));
+                } else {
+                    body.push_back("%r = arith.andi " + v + ", " + c15 + " : i8");
+                    out.push_back(mk(pointwise_generic(ind, g, u.in, u.in_ty.str(), id + ", " + id, r, e, half,
+                                                       "%b: i8, %o: i8", body)));
+                }
+                halves[hi] = g;
+            }
+            const std::string o = fresh("out"), i0 = fresh("interleaved");
+            out.push_back(mk(ind + o + " = tensor.empty() : " + full.str()));
+            out.push_back(mk(ind + i0 + " = tensor.insert_slice " + halves[0] + " into " + o + slice_spec(half, 0) + " : " +
+                             half.str() + " into " + full.str()));
+            out.push_back(mk(ind + s.result + " = tensor.insert_slice " + halves[1] + " into " + i0 + slice_spec(half, 1) +
+                             " : " + half.str() + " into " + full.str()));
+            if (def) dead_unpacks.insert(def->result);
+        }
+        f.body.swap(out);
+        std::vector<Stmt> kept;
+        for (const Stmt &s : f.body) {
+            if (s.op == "qf.unpack" && dead_unpacks.count(s.result) && !is_used_elsewhere(f, s.result, &s)) continue;
+            kept.push_back(s);
+        }
+        f.body.swap(kept);
+    }
+}
+
+// --lower-unpack-to-nvvm (lib/Transforms/LowerUnpackToNVVM.cpp:90-295) and --lower-unpack-to-prmt
+// (lib/Transforms/LowerUnpackToPRMT.cpp:293-350): scf.for over rows x 4-byte chunks; four bytes are read and
+// joined into one i32 word, the eight codes leave it LSB first (code n = (w >> 4n) & 0xF) and are written with
+// eight tensor.insert. Guards as in the reference: rank 2, static shape, doubling form, packed columns % 4 == 0.
+// The prmt variant spreads the codes to one byte each with two prmt.b32 on the nibble-masked words
+//   lo = w & 0x0F0F0F0F, hi = (w >> 4) & 0x0F0F0F0F, prmt(lo, hi, 0x5140) = codes 0..3, prmt(lo, hi, 0x7362) = 4..7
+// which is what the runtime's unpack kernel executes (the reference names the same two selectors but applies them
+// to the unmasked word with zero as second operand, which does not separate the nibbles on hardware).
+void pass_lower_unpack_loops(Module &mod, bool use_prmt) {
+    for (auto &c : mod.chunks) {
+        if (!c.is_func) continue;
+        Func &f = c.func;
+        std::vector<Stmt> out;
+        for (const Stmt &s : f.body) {
+            Unpack u;
+            if (s.op == "qf.unpack") u = parse_unpack(s);
+            const bool ok = u.ok && u.in_ty.elem == "i8" && u.in_ty.dims.size() == 2 && unpack_doubles(u) &&
+                            std::stoll(u.in_ty.dims[1]) % 4 == 0;
+            if (!ok) {
+                out.push_back(s);
+                continue;
+            }
+            const std::string ind = indent_of(s.text), i1 = ind + "  ", i2 = ind + "    ";
+            const std::string rows = u.in_ty.dims[0], chunks = std::to_string(std::stoll(u.in_ty.dims[1]) / 4);
+            const std::string in_t = u.in_ty.str(), out_t = u.out_ty.str();
+            const std::string e = fresh("init"), lb = fresh("c0"), st = fresh("c1"), ub0 = fresh("rows"), ub1 = fresh("chunks");
+            out.push_back(mk(ind + e + " = tensor.empty() : " + out_t));
+            out.push_back(mk(ind + lb + " = arith.constant 0 : index"));
+            out.push_back(mk(ind + st + " = arith.constant 1 : index"));
+            out.push_back(mk(ind + ub0 + " = arith.constant " + rows + " : index"));
+            out.push_back(mk(ind + ub1 + " = arith.constant " + chunks + " : index"));
+            std::string t = ind + s.result + " = scf.for %k = " + lb + " to " + ub0 + " step " + st + " iter_args(%acc_k = " + e +
+                            ") -> (" + out_t + ") {\n";
+            t += i1 + "%row = scf.for %ch = " + lb + " to " + ub1 + " step " + st + " iter_args(%acc = %acc_k) -> (" + out_t + ") {\n";
+            t += i2 + "%four = arith.constant 4 : index\n";
+            t += i2 + "%eight = arith.constant 8 : index\n";
+            t += i2 + "%col = arith.muli %ch, %four : index\n";
+            t += i2 + "%ocol = arith.muli %ch, %eight : index\n";
+            for (int b = 1; b < 4; ++b) {
+                t += i2 + "%off" + std::to_string(b) + " = arith.constant " + std::to_string(b) + " : index\n";
+                t += i2 + "%col" + std::to_string(b) + " = arith.addi %col, %off" + std::to_string(b) + " : index\n";
+            }
+            t += i2 + "%b0 = tensor.extract " + u.in + "[%k, %col] : " + in_t + "\n";
+            for (int b = 1; b < 4; ++b)
+                t += i2 + "%b" + std::to_string(b) + " = tensor.extract " + u.in + "[%k, %col" + std::to_string(b) + "] : " + in_t + "\n";
+            t += i2 + "%s8 = arith.constant 8 : i32\n";
+            t += i2 + "%s16 = arith.constant 16 : i32\n";
+            t += i2 + "%s24 = arith.constant 24 : i32\n";
+            for (int b = 0; b < 4; ++b)
+                t += i2 + "%e" + std::to_string(b) + " = arith.extui %b" + std::to_string(b) + " : i8 to i32\n";
+            t += i2 + "%h1 = arith.shli %e1, %s8 : i32\n";
+            t += i2 + "%w01 = arith.ori %e0, %h1 : i32\n";
+            t += i2 + "%h2 = arith.shli %e2, %s16 : i32\n";
+            t += i2 + "%w012 = arith.ori %w01, %h2 : i32\n";
+            t += i2 + "%h3 = arith.shli %e3, %s24 : i32\n";
+            t += i2 + "%w = arith.ori %w012, %h3 : i32\n";
+            if (!use_prmt) {
+                for (int n = 1; n < 8; ++n)
+                    t += i2 + "%sh" + std::to_string(n) + " = arith.constant " + std::to_string(4 * n) + " : i32\n";
+                t += i2 + "%mask = arith.constant 15 : i32\n";
+                for (int n = 0; n < 8; ++n) {
+                    const std::string ns = std::to_string(n);
+                    std::string src = "%w";
+                    if (n) {
+                        t += i2 + "%r" + ns + " = arith.shrui %w, %sh" + ns + " : i32\n";
+                        src = "%r" + ns;
+                    }
+                    t += i2 + "%m" + ns + " = arith.andi " + src + ", %mask : i32\n";
+                    t += i2 + "%q" + ns + " = arith.trunci %m" + ns + " : i32 to i8\n";
+                }
+            } else {
+                t += i2 + "%nib = arith.constant 252645135 : i32\n";  // 0x0F0F0F0F
+                t += i2 + "%four32 = arith.constant 4 : i32\n";
+                t += i2 + "%sel_lo = arith.constant 20800 : i32\n";   // 0x5140
+                t += i2 + "%sel_hi = arith.constant 29538 : i32\n";   // 0x7362
+                t += i2 + "%lo = arith.andi %w, %nib : i32\n";
+                t += i2 + "%wsh = arith.shrui %w, %four32 : i32\n";
+                t += i2 + "%hi = arith.andi %wsh, %nib : i32\n";
+                t += i2 + "%c0123 = llvm.inline_asm \"prmt.b32 $0, $1, $2, $3;\", \"=r,r,r,r\" %lo, %hi, %sel_lo : (i32, i32, i32) -> i32\n";
+                t += i2 + "%c4567 = llvm.inline_asm \"prmt.b32 $0, $1, $2, $3;\", \"=r,r,r,r\" %lo, %hi, %sel_hi : (i32, i32, i32) -> i32\n";
+                for (int b = 1; b < 4; ++b)
+                    t += i2 + "%bs" + std::to_string(b) + " = arith.constant " + std::to_string(8 * b) + " : i32\n";
+                for (int n = 0; n < 8; ++n) {
+                    const std::string ns = std::to_string(n), word = n < 4 ? "%c0123" : "%c4567";
+                    std::string src = word;
+                    if (n % 4) {
+                        t += i2 + "%r" + ns + " = arith.shrui " + word + ", %bs" + std::to_string(n % 4) + " : i32\n";
+                        src = "%r" + ns;
+                    }
+                    t += i2 + "%q" + ns + " = arith.trunci " + src + " : i32 to i8\n";
+                }
+            }
+            std::string acc = "%acc";
+            for (int n = 0; n < 8; ++n) {
+                const std::string ns = std::to_string(n);
+                std::string col = "%ocol";
+                if (n) {
+                    t += i2 + "%oo" + ns + " = arith.constant " + ns + " : index\n";
+                    t += i2 + "%oc" + ns + " = arith.addi %ocol, %oo" + ns + " : index\n";
+                    col = "%oc" + ns;
+                }
+                t += i2 + "%ins" + ns + " = tensor.insert %q" + ns + " into " + acc + "[%k, " + col + "] : " + out_t + "\n";
+                acc = "%ins" + ns;
+            }
+            t += i2 + "scf.yield " + acc + " : " + out_t + "\n";
+            t += i1 + "}\n";
+            t += i1 + "scf.yield %row : " + out_t + "\n";
+            t += ind + "}";
+            out.push_back(mk(t));
+        }
+        f.body.swap(out);
+    }
+}
+
+// --lower-dequant-to-arith (lib/Transforms/LowerDequantToArith.cpp:60-164): sitofp, sitofp, subf, mulf in f16
+// with the rank-0 scale and zero point broadcast.
+void pass_lower_dequant_to_arith(Module &mod) {
+    for (auto &c : mod.chunks) {
+        if (!c.is_func) continue;
+        Func &f = c.func;
+        std::vector<Stmt> out;
+        for (const Stmt &s : f.body) {
+            Dequant d;
+            if (s.op == "qf.dequant") d = parse_dequant(s);
+            if (!d.ok || d.out_ty.elem != "f16" || d.scale_ty != "tensor<f16>" || d.zp_ty != "tensor<i8>") {
+                out.push_back(s);
+                continue;
+            }
+            generic_dequant(indent_of(s.text), s.result, d.in, d, /*mask*/ false, /*zp*/ true, out);
+        }
+        f.body.swap(out);
+    }
+}
+
 const std::set<std::string> kReferenceOnlyPasses = {
-    "lower-unpack-to-arith", "lower-unpack-branch-free", "lower-unpack-to-nvvm", "lower-unpack-to-prmt",
-    "lower-dequant-to-arith", "fuse-unpack-dequant-branch-free", "register-layout-aware-unpack", "quantforge-tiling",
+    "register-layout-aware-unpack", "quantforge-tiling",
     "quantforge-vectorization", "quantforge-gpu-mapping", "quantforge-bufferize", "quantforge-smem-promotion",
     "quantforge-swizzle-load", "quantforge-lower-to-nvvm"};
 
@@ -835,9 +1164,21 @@ int main(int argc, char **argv) {
             pass_canonicalize_zp(mod);
         } else if (p.name == "lower-qf-to-runtime") {
             pass_lower_to_runtime(mod);
+        } else if (p.name == "lower-unpack-to-arith") {
+            pass_lower_unpack_to_arith(mod);
+        } else if (p.name == "lower-unpack-branch-free") {
+            pass_branch_free(mod, false);
+        } else if (p.name == "fuse-unpack-dequant-branch-free") {
+            pass_branch_free(mod, true);
+        } else if (p.name == "lower-unpack-to-nvvm") {
+            pass_lower_unpack_loops(mod, false);
+        } else if (p.name == "lower-unpack-to-prmt") {
+            pass_lower_unpack_loops(mod, true);
+        } else if (p.name == "lower-dequant-to-arith") {
+            pass_lower_dequant_to_arith(mod);
         } else if (kReferenceOnlyPasses.count(p.name)) {
-            die("pass '" + p.name + "' is not part of this build (it lowers to scalar arithmetic; the runtime build "
-                "lowers the same ops with --lower-qf-to-runtime)");
+            die("pass '" + p.name + "' is not part of this build (generic GPU code generation scaffolding: tile shapes, "
+                "staging, swizzle and launch geometry live inside the hand-written kernels)");
         } else {
             die("unknown pass '" + p.name + "'");
         }

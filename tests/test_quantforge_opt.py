@@ -108,7 +108,7 @@ def test_no_fallback_and_unknown_passes_fail(opt):
     # a qf.dequant on a plain tensor cannot become a runtime call: the pass fails (exit 1), nothing is emulated
     _, err = run(opt, ["--lower-qf-to-runtime"], "ops.mlir", expect=1)
     assert "no CPU fallback" in err
-    _, err = run(opt, ["--lower-unpack-to-arith"], "ops.mlir", expect=1)
+    _, err = run(opt, ["--quantforge-tiling"], "ops.mlir", expect=1)
     assert "not part of this build" in err
     run(opt, ["--no-such-pass"], "ops.mlir", expect=1)
 
@@ -129,3 +129,43 @@ def test_fold_subf_zero(opt):
     out, _ = run(opt, ["--canonicalize-dequant-zp"], "unpack_dequant.mlir")
     body = func_body(out, "fold_subf_zero")
     assert "arith.subf" not in body and "return %x : f16" in body
+
+
+def test_scalar_lowerings_of_unpack_and_dequant(opt):
+    """The reference's scalar lowerings under their own flag names (the arithmetic the kernels implement)."""
+    out, _ = run(opt, ["--lower-unpack-to-arith"], "unpack_dequant.mlir")
+    assert re.search(r"^#map\d* = affine_map<\(d0, d1, d2\) -> \(d0, d1\)>", out, re.M)
+    body = func_body(out, "unpack_only")
+    assert "qf.unpack" not in body
+    check_order(body, [r"arith\.constant 15 : i8", r"arith\.constant 4 : i8", r"tensor\.empty\(\) : tensor<4096x2048x2xi8>",
+                       r"linalg\.generic \{indexing_maps = \[#map\d*, #map\d*\]", r"arith\.andi", r"arith\.shrui",
+                       r"arith\.andi", r"arith\.select", r"linalg\.yield",
+                       r"tensor\.collapse_shape %\S+ \[\[0\], \[1, 2\]\] : tensor<4096x2048x2xi8> into tensor<4096x4096xi8>"])
+
+    out, _ = run(opt, ["--lower-unpack-branch-free"], "unpack_dequant.mlir")
+    body = func_body(out, "unpack_only")
+    assert "qf.unpack" not in body and "arith.select" not in body and "linalg.index" not in body
+    check_order(body, [r"linalg\.generic", r"arith\.andi %b", r"linalg\.generic", r"arith\.shrui %b", r"arith\.andi",
+                       r"tensor\.insert_slice %\S+ into %\S+\[0, 0\] \[4096, 2048\] \[1, 2\]",
+                       r"tensor\.insert_slice %\S+ into %\S+\[0, 1\] \[4096, 2048\] \[1, 2\]"])
+
+    for flag, marks in (("--lower-unpack-to-nvvm", [r"arith\.shrui", r"arith\.andi", r"arith\.trunci"]),
+                        ("--lower-unpack-to-prmt", [r'llvm\.inline_asm "prmt\.b32', r'llvm\.inline_asm "prmt\.b32',
+                                                    r"arith\.trunci"])):
+        out, _ = run(opt, [flag], "unpack_dequant.mlir")
+        body = func_body(out, "unpack_only")
+        assert "qf.unpack" not in body and "linalg.generic" not in body
+        check_order(body, [r"scf\.for", r"scf\.for"] + [r"tensor\.extract"] * 4 +
+                    [r"arith\.extui", r"arith\.shli", r"arith\.ori"] + marks + [r"tensor\.insert "] * 8 + [r"scf\.yield"])
+
+    out, _ = run(opt, ["--lower-dequant-to-arith"], "unpack_dequant.mlir")
+    body = func_body(out, "unpack_dequant")
+    assert "qf.dequant" not in body and "qf.unpack" in body
+    check_order(body, [r"linalg\.generic", r"arith\.sitofp %\S+ : i8 to f16", r"arith\.sitofp %\S+ : i8 to f16",
+                       r"arith\.subf", r"arith\.mulf", r"linalg\.yield"])
+
+    out, _ = run(opt, ["--fuse-unpack-dequant-branch-free"], "unpack_dequant.mlir")
+    body = func_body(out, "unpack_dequant")
+    assert "qf." not in body and "arith.select" not in body
+    check_order(body, [r"linalg\.generic", r"arith\.sitofp", r"linalg\.generic", r"arith\.shrui", r"arith\.sitofp",
+                       r"tensor\.insert_slice .*\[0, 0\].*\[1, 2\]", r"tensor\.insert_slice .*\[0, 1\].*\[1, 2\]"])
