@@ -58,6 +58,7 @@ struct SlabParams {
     int m_pad;                  // batch rows a stage has room for: 1, 2, 4, 8, 16 or 32
     int out_dtype;
     int epilogue;
+    int stream_only;            // measurement aid: consumers release every stage unread (see launch_gemv_slab_impl)
 };
 
 // Shared-memory loads with the constant part of the address as an immediate (no address arithmetic in the loop).
@@ -345,6 +346,21 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
         if (!__all_sync(0xffffffffu, ok)) {
             aborted = true;
             break;
+        }
+        if (p.stream_only) {
+            // bandwidth ceiling of the copy pipeline alone: nothing is converted or multiplied
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ebar);
+            if (++s == p.depth) {
+                s = 0;
+                ph ^= 1u;
+                fbar = full_bar(0);
+                ebar = empty_bar(0);
+            } else {
+                fbar += 8u;
+                ebar += 8u;
+            }
+            continue;
         }
         const uint4 va = lds128_at<0>(wptr);
         const uint4 vb = lds128_at<512>(wptr);
@@ -737,6 +753,11 @@ static int launch_gemv_slab_impl(qf_ctx *ctx, const qf_linear_desc *d, const Pla
     p.m_pad = slab_m_pad(d->M);
     p.out_dtype = d->out_dtype;
     p.epilogue = ar ? QF_EPI_NONE : d->epilogue;
+    // QF_SLAB_STREAM_ONLY=1 (measurement only): the kernel moves every byte through its copy pipeline but converts
+    // and multiplies nothing, so Y is NOT computed. It exists to time the ceiling the weight stream alone allows for
+    // a given shape under the same launch sequence (graph, programmatic dependent launch) as the real kernel.
+    const char *so = std::getenv("QF_SLAB_STREAM_ONLY");
+    p.stream_only = (so && so[0] == '1') ? 1 : 0;
     const dim3 grid((unsigned)plan.split_k), blk(SLAB_THREADS);
     const size_t smem = slab_smem_bytes(p.depth, p.m_pad);
     const bool pdl = pdl_enabled();
