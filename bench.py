@@ -268,7 +268,7 @@ def oracle_silu_mul(gate, up):
 # ------------------------------------------------------------------------------------------------
 # single-GPU extras: the sweep per case, cfg0, cfg2, cfg3, K1 bandwidth
 # ------------------------------------------------------------------------------------------------
-def time_case(env, M, K, N, act, out_dt, sym, sigma, slab, copies=None, reps=5, gen=None):
+def time_case(env, M, K, N, act, out_dt, sym, sigma, slab, copies=None, reps=5, gen=None, stream_only=False):
     """One linear as a CUDA graph of one launch per weight copy, with enough copies (>= 300 MB) that every launch
     reads its weights from HBM; the figure is the average launch-to-launch time inside the graph (best of `reps`)."""
     torch, qf, dev = env.torch, env.qf, env.dev
@@ -299,12 +299,19 @@ def time_case(env, M, K, N, act, out_dt, sym, sigma, slab, copies=None, reps=5, 
         else:
             qf.w4a16_linear(x, qw, sc, zr, group_size=GROUP, zero_const=8, out=y, out_dtype=out_dt,
                             weight_layout=layout)
-    run(0)
-    torch.cuda.synchronize()
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
-        for i in range(n):
-            run(i)
+    if stream_only:
+        # measurement mode of the slab kernel (read at launch, i.e. at capture): weights go through the copy pipeline,
+        # nothing is converted or multiplied - the ceiling the weight stream alone allows in this very harness
+        os.environ["QF_SLAB_STREAM_ONLY"] = "1"
+    try:
+        run(0)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(n):
+                run(i)
+    finally:
+        os.environ.pop("QF_SLAB_STREAM_ONLY", None)
     best = None
     for it in range(reps + 2):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -355,10 +362,23 @@ def single_gpu_extras(env, args):
     b = algo_bytes(1, 4096, 4096)
     us = time_case(env, 1, 4096, 4096, torch.float16, torch.float16, False, 0.02, True, gen=gen)
     us_old = time_case(env, 1, 4096, 4096, torch.float16, torch.float16, False, 0.02, False, gen=gen)
+    us_read = time_case(env, 1, 4096, 4096, torch.float16, torch.float16, False, 0.02, True, gen=gen, stream_only=True)
     extra["cfg0_gemv_m1_4096x4096_f16"] = {
         "us": round(us, 2), "gbs": round(b / us / 1e3, 1), "frac_hbm": round(b / us / 1e3 / hbm, 3),
         "kernel": "qf::gemv_slab_kernel (prepacked slab)",
-        "canonical_weights_gemv_kernel_us": round(us_old, 2)}
+        "canonical_weights_gemv_kernel_us": round(us_old, 2),
+        "weight_stream_only_us": round(us_read, 2),
+        "weight_stream_only_frac_hbm": round(b / us_read / 1e3 / hbm, 3),
+        "note": "weight_stream_only = the same launches in the same graph with the kernel moving its bytes through "
+                "the bulk-copy pipeline and doing no arithmetic: the ceiling of a dependent-launch GEMV of this size"}
+    bb = algo_bytes(1, 8192, 57344)
+    us_big = time_case(env, 1, 8192, 57344, torch.bfloat16, torch.bfloat16, False, 0.02, True, copies=2, gen=gen)
+    us_big_read = time_case(env, 1, 8192, 57344, torch.bfloat16, torch.bfloat16, False, 0.02, True, copies=2, gen=gen,
+                            stream_only=True)
+    extra["gemv_m1_8192x57344_bf16_70b_gate_up"] = {
+        "us": round(us_big, 2), "gbs": round(bb / us_big / 1e3, 1), "frac_hbm": round(bb / us_big / 1e3 / hbm, 3),
+        "weight_stream_only_us": round(us_big_read, 2),
+        "weight_stream_only_frac_hbm": round(bb / us_big_read / 1e3 / hbm, 3)}
     from quantforge_b200 import stack as S
     for bsz in (1, 16):
         for mode in ("fused", "fused_epilogues"):

@@ -339,16 +339,11 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
     }
     const uint32_t wrap_back = (uint32_t)(p.depth - 1) * stage_bytes;
 
-#pragma unroll 1
-    for (int it = 0; it < n_units; ++it) {
-        bool ok = mbar_try_wait(fbar, ph) != 0;
-        if (!ok) ok = mbar_wait(fbar, ph, abort_flag);
-        if (!__all_sync(0xffffffffu, ok)) {
-            aborted = true;
-            break;
-        }
-        if (p.stream_only) {
-            // bandwidth ceiling of the copy pipeline alone: nothing is converted or multiplied
+    if (p.stream_only) {
+        // measurement aid: the bandwidth ceiling of the copy pipeline alone. Every stage is released unread; nothing is
+        // converted, multiplied or written.
+        for (int it = 0; it < n_units; ++it) {
+            if (!mbar_wait(fbar, ph, abort_flag)) break;
             __syncwarp();
             if (lane == 0) mbar_arrive(ebar);
             if (++s == p.depth) {
@@ -360,7 +355,17 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
                 fbar += 8u;
                 ebar += 8u;
             }
-            continue;
+        }
+        return;
+    }
+
+#pragma unroll 1
+    for (int it = 0; it < n_units; ++it) {
+        bool ok = mbar_try_wait(fbar, ph) != 0;
+        if (!ok) ok = mbar_wait(fbar, ph, abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) {
+            aborted = true;
+            break;
         }
         const uint4 va = lds128_at<0>(wptr);
         const uint4 vb = lds128_at<512>(wptr);
