@@ -194,8 +194,11 @@ int qf_w4a16_linear_host(qf_ctx *ctx, const qf_linear_desc *desc, const void *X_
  * The same without the final wait: the copies and the kernel are enqueued on `stream` and the call returns.
  * Y_host holds the result once the caller has synchronised `stream`; X_host must stay unchanged until then.
  * Use page-locked host buffers (with pageable ones the copies block the host anyway). Calls on one stream may be
- * issued back to back: they share the context's staging buffers in stream order. Calls on different streams of
- * one context must not overlap.
+ * issued back to back: the context keeps two staging slots and copies the activations of a call on a stream of its
+ * own, so that they cross PCIe while the previous call's kernel runs; results return on `stream`. The slot written by
+ * call i+2 holds Y of call i until that call's copy back has been enqueued on `stream`, which stream order guarantees.
+ * Calls on different streams of one context must not overlap. Staging grows on first use of a larger shape
+ * (a device allocation); outgrown buffers are released with the context.
  */
 int qf_w4a16_linear_host_async(qf_ctx *ctx, const qf_linear_desc *desc, const void *X_host, const void *qweight,
                          const void *scales, const void *qzeros_or_null, void *Y_host, void *workspace,

@@ -277,8 +277,15 @@ int qf_ctx_create(qf_ctx **out, int device) {
 int qf_ctx_destroy(qf_ctx *ctx) {
     if (!ctx) return QF_OK;
     DeviceGuard guard(ctx->device);
-    if (ctx->stage_x) cudaFree(ctx->stage_x);
-    if (ctx->stage_y) cudaFree(ctx->stage_y);
+    cudaDeviceSynchronize();
+    for (auto &sl : ctx->host_slot) {
+        if (sl.x) cudaFree(sl.x);
+        if (sl.y) cudaFree(sl.y);
+        if (sl.copied_in) cudaEventDestroy(sl.copied_in);
+        if (sl.kernel_done) cudaEventDestroy(sl.kernel_done);
+    }
+    for (void *q : ctx->retired) cudaFree(q);
+    if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
     if (ctx->host_status) cudaFreeHost(ctx->host_status);
     delete ctx;
     return QF_OK;
@@ -468,13 +475,12 @@ int qf_w4a16_gemv_static_scratch(qf_ctx *ctx, const qf_linear_desc *desc, const 
     return launch_gemv_static(ctx, &d, plan, X, qweight, scales, qzeros_or_null, Y, (cudaStream_t)stream);
 }
 
+// Staging buffers only grow; the outgrown one is retired, not freed (see qf_ctx::HostSlot).
 static int grow(qf_ctx *ctx, void **buf, size_t *have, size_t need) {
     if (*have >= need) return QF_OK;
-    if (*buf) {
-        QF_CUDA_TRY(ctx, cudaFree(*buf));
-        *buf = nullptr;
-        *have = 0;
-    }
+    if (*buf) ctx->retired.push_back(*buf);
+    *buf = nullptr;
+    *have = 0;
     size_t cap = (need + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
     QF_CUDA_TRY(ctx, cudaMalloc(buf, cap));
     *have = cap;
@@ -489,18 +495,35 @@ int qf_w4a16_linear_host_async(qf_ctx *ctx, const qf_linear_desc *desc, const vo
     if (!X_host || !Y_host) return fail(ctx, QF_ERR_BAD_ARG, "null host pointer");
     if (desc->M == 0) return QF_OK;
     if (desc->M < 0 || desc->N <= 0 || desc->K <= 0) return fail(ctx, QF_ERR_BAD_ARG, "bad shape");
-    const size_t xb = (size_t)desc->M * desc->K * 2;
-    const size_t yb = (size_t)desc->M * desc->N * (desc->out_dtype == QF_F32 ? 4 : 2);
-    int st = grow(ctx, &ctx->stage_x, &ctx->stage_x_bytes, xb);
+    int st = check_current_device(ctx);
     if (st != QF_OK) return st;
-    st = grow(ctx, &ctx->stage_y, &ctx->stage_y_bytes, yb);
+    const size_t xb = (size_t)desc->M * desc->K * 2;
+    const int64_t out_cols = desc->epilogue == QF_EPI_SILU_MUL ? desc->N / 2 : desc->N;
+    const size_t yb = (size_t)desc->M * out_cols * (desc->out_dtype == QF_F32 ? 4 : 2);
+    if (!ctx->copy_stream) {
+        QF_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+        for (auto &sl : ctx->host_slot) {
+            QF_CUDA_TRY(ctx, cudaEventCreateWithFlags(&sl.copied_in, cudaEventDisableTiming));
+            QF_CUDA_TRY(ctx, cudaEventCreateWithFlags(&sl.kernel_done, cudaEventDisableTiming));
+        }
+    }
+    qf_ctx::HostSlot &sl = ctx->host_slot[ctx->host_next];
+    ctx->host_next ^= 1;
+    st = grow(ctx, &sl.x, &sl.x_bytes, xb);
+    if (st != QF_OK) return st;
+    st = grow(ctx, &sl.y, &sl.y_bytes, yb);
     if (st != QF_OK) return st;
     cudaStream_t s = (cudaStream_t)stream;
-    QF_CUDA_TRY(ctx, cudaMemcpyAsync(ctx->stage_x, X_host, xb, cudaMemcpyHostToDevice, s));
-    st = qf_w4a16_linear(ctx, desc, ctx->stage_x, qweight, scales, qzeros_or_null, ctx->stage_y, workspace,
-                         workspace_bytes, stream);
+    // activations: on the copy stream, as soon as the slot's previous kernel (two calls ago) has read its own
+    QF_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->copy_stream, sl.kernel_done, 0));  // no-op before the first record
+    QF_CUDA_TRY(ctx, cudaMemcpyAsync(sl.x, X_host, xb, cudaMemcpyHostToDevice, ctx->copy_stream));
+    QF_CUDA_TRY(ctx, cudaEventRecord(sl.copied_in, ctx->copy_stream));
+    QF_CUDA_TRY(ctx, cudaStreamWaitEvent(s, sl.copied_in, 0));
+    st = qf_w4a16_linear(ctx, desc, sl.x, qweight, scales, qzeros_or_null, sl.y, workspace, workspace_bytes, stream);
     if (st != QF_OK) return st;
-    QF_CUDA_TRY(ctx, cudaMemcpyAsync(Y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, s));
+    QF_CUDA_TRY(ctx, cudaEventRecord(sl.kernel_done, s));
+    // the result goes back on the caller's stream: synchronising it is all the caller has to do
+    QF_CUDA_TRY(ctx, cudaMemcpyAsync(Y_host, sl.y, yb, cudaMemcpyDeviceToHost, s));
     return QF_OK;
 }
 

@@ -9,6 +9,7 @@
 #include <atomic>
 #include <string>
 #include <utility>
+#include <vector>
 
 #include "quantforge_rt.h"
 
@@ -25,11 +26,22 @@ struct qf_ctx {
     int device = 0;
     int sm_count = 148;
     std::string last_error;
-    // staging for the *_host entry points (grown on demand, freed with the context)
-    void *stage_x = nullptr;
-    size_t stage_x_bytes = 0;
-    void *stage_y = nullptr;
-    size_t stage_y_bytes = 0;
+    // Staging for the *_host entry points: two slots used in turn, so that the activations of call i+1 cross PCIe (on
+    // the context's own copy stream) while the kernel of call i runs. Buffers only ever grow; a buffer that became
+    // too small is kept until the context is destroyed (kernels enqueued earlier may still use it, and freeing
+    // would synchronise the device in the middle of a hot call).
+    struct HostSlot {
+        void *x = nullptr;
+        size_t x_bytes = 0;
+        void *y = nullptr;
+        size_t y_bytes = 0;
+        cudaEvent_t copied_in = nullptr;   // activations of the slot's latest call are on the device
+        cudaEvent_t kernel_done = nullptr; // its kernel has read them
+    };
+    HostSlot host_slot[2];
+    int host_next = 0;
+    cudaStream_t copy_stream = nullptr;
+    std::vector<void *> retired;  // outgrown staging buffers
     // device status word written by kernels whose bounded waits expire (tcgen05 path)
     int *dev_status = nullptr;
     int *host_status = nullptr;  // pinned mirror

@@ -292,9 +292,11 @@ def test_ranks_exchange_inside_the_kernels(world):
     procs = [ctx.Process(target=_worker, args=(r, world, port, out)) for r in range(world)]
     for p in procs:
         p.start()
+    import time
+    deadline = time.time() + 300  # one deadline for all ranks together
     codes = []
     for p in procs:
-        p.join(300)
+        p.join(max(1.0, deadline - time.time()))
         if p.is_alive():  # never leave a straggler behind on a shared GPU
             p.terminate()
             p.join(30)

@@ -71,9 +71,11 @@ def test_column_then_row_parallel(world):
     procs = [ctx.Process(target=_worker, args=(r, world, port, out)) for r in range(world)]
     for p in procs:
         p.start()
+    import time
+    deadline = time.time() + 300  # one deadline for all ranks together
     codes = []
     for p in procs:
-        p.join(300)
+        p.join(max(1.0, deadline - time.time()))
         if p.is_alive():
             p.terminate()
             p.join(30)
