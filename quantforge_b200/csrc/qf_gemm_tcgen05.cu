@@ -438,6 +438,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(afull_bar(a));
+            fence_proxy_async_shared();  // this thread's reads of the stage, before the copy engine refills it
             mbar_arrive(empty_bar(s));
         }
 

@@ -393,6 +393,11 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
         step(std::integral_constant<int, 1>{});
         step(std::integral_constant<int, 2>{});
         step(std::integral_constant<int, 3>{});
+        // The stage is refilled by the copy engine (async proxy) once the four warps have released it, and the
+        // reads above went through the generic proxy: the proxy fence orders them before the release. Without it the
+        // last activation read of a step was observed to return the refill's data (thread blocks that start while
+        // the memory system is lightly loaded, where a refill lands within a few hundred nanoseconds).
+        fence_proxy_async_shared();
         __syncwarp();
         if (lane == 0) mbar_arrive(ebar);
         if (++s == p.depth) {

@@ -30,6 +30,13 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok;
 }
 
+// Orders this thread's earlier shared-memory accesses made with ordinary loads and stores (generic proxy) before
+// later accesses of the copy engine and the tensor cores (async proxy) to the same memory. Needed on both sides of a
+// staging buffer: after writing data that the async proxy will read, and after reading data that it will overwrite.
+__device__ __forceinline__ void fence_proxy_async_shared() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 // Bounded wait. Returns false on expiry or when another role aborted.
 // A waiting warp backs off with nanosleep so that its polling does not take issue slots from the warps
 // that convert; the sleep is short next to the time a pipeline step takes.
