@@ -220,8 +220,8 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
     const uint32_t ring = (smem_u32(slab_smem) + 127u) & ~127u;
     const uint32_t bar_base = ring + (uint32_t)p.depth * stage_bytes;
     auto stage = [&](int s) { return ring + (uint32_t)s * stage_bytes; };
-    auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(p.depth + s); };
+    auto full_bar = [&](int s) { return bar_base + 16u * (uint32_t)s; };
+    auto empty_bar = [&](int s) { return bar_base + 16u * (uint32_t)s + 8u; };
 
     const long long G = gridDim.x;
     const long long cta = blockIdx.x;
@@ -326,7 +326,7 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
     // Ring position and addresses advance incrementally (no division by the run-time depth in the loop).
     int s = 0;
     uint32_t ph = 0;
-    uint32_t fbar = full_bar(0), ebar = empty_bar(0);
+    uint32_t fbar = full_bar(0);
     uint32_t wptr = stage(0) + (uint32_t)warp * SLAB_TILE_BYTES + (uint32_t)lane * 16u;  // this lane's codes
     const uint32_t cst_off = 1024u + (uint32_t)g * 4u - (uint32_t)lane * 16u;            // -> its row's constants
     uint32_t x_off[MT];                                                                  // -> its activation rows
@@ -337,7 +337,9 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
         x_off[nt] = (uint32_t)SLAB_UNIT_BYTES - (uint32_t)warp * SLAB_TILE_BYTES - (uint32_t)lane * 16u +
                     (uint32_t)t * 16u + row * SLAB_X_PITCH;
     }
-    const uint32_t wrap_back = (uint32_t)(p.depth - 1) * stage_bytes;
+    const uint32_t ring_bytes = (uint32_t)p.depth * stage_bytes;
+    const uint32_t bars_bytes = 16u * (uint32_t)p.depth;
+    int seg_left = min(p.chunks - c, n_units);
 
     if (p.stream_only) {
         // measurement aid: the bandwidth ceiling of the copy pipeline alone. Every stage is released unread; nothing is
@@ -345,15 +347,12 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
         for (int it = 0; it < n_units; ++it) {
             if (!mbar_wait(fbar, ph, abort_flag)) break;
             __syncwarp();
-            if (lane == 0) mbar_arrive(ebar);
+            if (lane == 0) mbar_arrive(fbar + 8u);
+            fbar += 16u;
             if (++s == p.depth) {
                 s = 0;
                 ph ^= 1u;
                 fbar = full_bar(0);
-                ebar = empty_bar(0);
-            } else {
-                fbar += 8u;
-                ebar += 8u;
             }
         }
         return;
@@ -399,20 +398,17 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
         // the memory system is lightly loaded, where a refill lands within a few hundred nanoseconds).
         fence_proxy_async_shared();
         __syncwarp();
-        if (lane == 0) mbar_arrive(ebar);
+        if (lane == 0) mbar_arrive_at<8>(fbar);  // the stage's empty barrier sits right behind its full barrier
+        wptr += stage_bytes;
+        fbar += 16u;
         if (++s == p.depth) {
             s = 0;
             ph ^= 1u;
-            wptr -= wrap_back;
-            fbar = full_bar(0);
-            ebar = empty_bar(0);
-        } else {
-            wptr += stage_bytes;
-            fbar += 8u;
-            ebar += 8u;
+            wptr -= ring_bytes;
+            fbar -= bars_bytes;
         }
         ++c;
-        if (c == p.chunks || it == n_units - 1) {
+        if (--seg_left == 0) {
             // end of this block's share of row block b
             float v[MT][4];
 #pragma unroll
@@ -451,6 +447,7 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
                 ++b;
             }
             c_lo = c;
+            seg_left = min(p.chunks - c, n_units - 1 - it);
         }
     }
 
