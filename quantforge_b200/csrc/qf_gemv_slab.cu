@@ -10,10 +10,11 @@
 // count, so the whole launch is resident at once.
 //
 // Inside a block (160 threads):
-//   warp 4      producer: one cp.async.bulk per unit into a ring of shared-memory stages (full / empty mbarriers),
-//               plus one 256-byte bulk copy per batch row for the unit's slice of X. All weight copies of the
-//               first pass over the ring are issued BEFORE the programmatic-dependent-launch wait (weights do not
-//               depend on the previous kernel of the stream), the activation copies after it.
+//   warp 4      producer: one cp.async.bulk per PAIR of consecutive units (8704 contiguous bytes of the blob) into a
+//               ring of shared-memory stages (full / empty mbarriers), plus one 512-byte bulk copy per batch row for
+//               the pair's slices of X (two of 256 bytes where the pair straddles a row block). All weight copies of
+//               the first pass over the ring are issued BEFORE the programmatic-dependent-launch wait (weights do
+//               not depend on the previous kernel of the stream), the activation copies after it.
 //   warps 0-3   consumers: warp w owns rows 16w..16w+15 of the unit. Per unit and lane: 2 x 16 B of codes and two
 //               constants words from shared memory -> lop3 / packed 16-bit arithmetic -> A fragments of
 //               m16n8k16 tensor-core MMAs; B fragments are 16-byte reads of the natural-order activation slice
@@ -39,7 +40,7 @@ namespace qf {
 constexpr int SLAB_THREADS = 160;
 constexpr int SLAB_TILE_BYTES = 1088;           // 2 x 512 B of codes + 64 B of constants
 constexpr int SLAB_UNIT_BYTES = QF_SLAB_UNIT_BYTES;
-constexpr int SLAB_X_PITCH = 320;               // bytes between batch rows of a stage's activation slice (256 + 64
+constexpr int SLAB_X_PITCH = 576;               // bytes between batch rows of a stage's activation slices (2 x 256 + 64
                                                 // of skew: rows g and g+1 land in different shared-memory banks)
 constexpr int SLAB_MAX_DEPTH = 16;
 static_assert(SLAB_UNIT_BYTES == 4 * SLAB_TILE_BYTES, "unit = 4 tiles");
@@ -216,7 +217,7 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const uint32_t stage_bytes = (uint32_t)SLAB_UNIT_BYTES + (uint32_t)p.m_pad * SLAB_X_PITCH;
+    const uint32_t stage_bytes = 2u * SLAB_UNIT_BYTES + (uint32_t)p.m_pad * SLAB_X_PITCH;
     const uint32_t ring = (smem_u32(slab_smem) + 127u) & ~127u;
     const uint32_t bar_base = ring + (uint32_t)p.depth * stage_bytes;
     auto stage = [&](int s) { return ring + (uint32_t)s * stage_bytes; };
@@ -227,6 +228,7 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
     const long long cta = blockIdx.x;
     const long long u0 = cta * p.units / G;
     const int n_units = (int)((cta + 1) * p.units / G - u0);
+    const int n_pairs = (n_units + 1) >> 1;
     volatile int *abort_flag = &s_abort;
 
     if (tid == 0) {
@@ -242,43 +244,55 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
 
     if (warp == 4) {
         // ------------------------------ producer ------------------------------
+        // A stage holds a PAIR of consecutive units (contiguous in the blob: one bulk copy) and their activation
+        // slices; the last pair of an odd range holds one unit.
         const int M = (int)p.M;
-        const uint32_t tx = (uint32_t)SLAB_UNIT_BYTES + (uint32_t)M * 256u;
         const uint8_t *src = p.blob + (size_t)u0 * SLAB_UNIT_BYTES;
-        const int npre = min(p.depth, n_units);
+        const int npre = min(p.depth, n_pairs);
         int issued = 0;
-        if (lane == 0)
-            for (int it = 0; it < npre; ++it) {
-                mbar_arrive_expect_tx(full_bar(it), tx);
-                bulk_load(stage(it), src + (size_t)it * SLAB_UNIT_BYTES, SLAB_UNIT_BYTES, full_bar(it));
+        auto pair_units = [&](int ip) { return min(2, n_units - 2 * ip); };
+        auto issue_w = [&](int ip, int s) {  // lane 0
+            const uint32_t nu = (uint32_t)pair_units(ip);
+            mbar_arrive_expect_tx(full_bar(s), nu * ((uint32_t)SLAB_UNIT_BYTES + (uint32_t)M * 256u));
+            bulk_load(stage(s), src + (size_t)ip * (2 * SLAB_UNIT_BYTES), nu * (uint32_t)SLAB_UNIT_BYTES, full_bar(s));
+        };
+        auto issue_x = [&](int ip, int s, int c) {  // lanes < M; c = K chunk of the pair's first unit
+            const uint32_t dst = stage(s) + 2u * SLAB_UNIT_BYTES + (uint32_t)lane * SLAB_X_PITCH;
+            const uint16_t *row = p.X + (size_t)lane * p.K;
+            const int nu = pair_units(ip);
+            if (nu == 2 && c + 1 < p.chunks) {
+                bulk_load(dst, row + (size_t)c * 128, 512u, full_bar(s));
+            } else {
+                bulk_load(dst, row + (size_t)c * 128, 256u, full_bar(s));
+                if (nu == 2) bulk_load(dst + 256u, row, 256u, full_bar(s));  // first chunk of the next row block
             }
+        };
+        if (lane == 0)
+            for (int ip = 0; ip < npre; ++ip) issue_w(ip, ip);
         __syncwarp();
         griddep_wait();  // the activations are the previous kernel's output
         int c = (int)(u0 % p.chunks);
-        for (int it = 0; it < npre; ++it) {
-            if (lane < M)
-                bulk_load(stage(it) + SLAB_UNIT_BYTES + (uint32_t)lane * SLAB_X_PITCH,
-                          p.X + (size_t)lane * p.K + (size_t)c * 128, 256u, full_bar(it));
-            if (++c == p.chunks) c = 0;
+        auto advance_c = [&]() {
+            c += 2;
+            while (c >= p.chunks) c -= p.chunks;
+        };
+        for (int ip = 0; ip < npre; ++ip) {
+            if (lane < M) issue_x(ip, ip, c);
+            advance_c();
         }
         issued = npre;
         // steady state: ring position advances incrementally (npre == depth whenever this loop runs)
         int s = 0;
         uint32_t ph = 0;  // parity of the consumers' previous pass over stage s
-        for (int it = npre; it < n_units; ++it) {
+        for (int ip = npre; ip < n_pairs; ++ip) {
             bool ok = mbar_try_wait(empty_bar(s), ph) != 0;
             if (!ok) ok = mbar_wait(empty_bar(s), ph, abort_flag);
             if (!__all_sync(0xffffffffu, ok)) break;
-            if (lane == 0) {
-                mbar_arrive_expect_tx(full_bar(s), tx);
-                bulk_load(stage(s), src + (size_t)it * SLAB_UNIT_BYTES, SLAB_UNIT_BYTES, full_bar(s));
-            }
+            if (lane == 0) issue_w(ip, s);
             __syncwarp();
-            if (lane < M)
-                bulk_load(stage(s) + SLAB_UNIT_BYTES + (uint32_t)lane * SLAB_X_PITCH,
-                          p.X + (size_t)lane * p.K + (size_t)c * 128, 256u, full_bar(s));
-            if (++c == p.chunks) c = 0;
-            issued = it + 1;
+            if (lane < M) issue_x(ip, s, c);
+            advance_c();
+            issued = ip + 1;
             if (++s == p.depth) {
                 s = 0;
                 ph ^= 1u;
@@ -288,8 +302,8 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
             // drain this block's own copies before its shared memory goes away (the consumers stopped waiting)
             int dummy = 0;
             volatile int *no_abort = &dummy;
-            for (int it = max(0, issued - p.depth); it < issued; ++it)
-                mbar_wait(full_bar(it % p.depth), (uint32_t)(it / p.depth) & 1u, no_abort);
+            for (int ip = max(0, issued - p.depth); ip < issued; ++ip)
+                mbar_wait(full_bar(ip % p.depth), (uint32_t)(ip / p.depth) & 1u, no_abort);
             if (lane == 0) atomicExch(p.status, QF_ERR_TIMEOUT);
         }
         return;
@@ -334,7 +348,7 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
     for (int nt = 0; nt < MT; ++nt) {
         // batch rows beyond m_pad are never stored: wrap into the rows the stage holds
         const uint32_t row = (uint32_t)((nt * 8 + g) & (p.m_pad - 1));
-        x_off[nt] = (uint32_t)SLAB_UNIT_BYTES - (uint32_t)warp * SLAB_TILE_BYTES - (uint32_t)lane * 16u +
+        x_off[nt] = 2u * SLAB_UNIT_BYTES - (uint32_t)warp * SLAB_TILE_BYTES - (uint32_t)lane * 16u +
                     (uint32_t)t * 16u + row * SLAB_X_PITCH;
     }
     const uint32_t ring_bytes = (uint32_t)p.depth * stage_bytes;
@@ -344,7 +358,7 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
     if (p.stream_only) {
         // measurement aid: the bandwidth ceiling of the copy pipeline alone. Every stage is released unread; nothing is
         // converted, multiplied or written.
-        for (int it = 0; it < n_units; ++it) {
+        for (int ip = 0; ip < n_pairs; ++ip) {
             if (!mbar_wait(fbar, ph, abort_flag)) break;
             __syncwarp();
             if (lane == 0) mbar_arrive(fbar + 8u);
@@ -358,19 +372,16 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
         return;
     }
 
-#pragma unroll 1
-    for (int it = 0; it < n_units; ++it) {
-        bool ok = mbar_try_wait(fbar, ph) != 0;
-        if (!ok) ok = mbar_wait(fbar, ph, abort_flag);
-        if (!__all_sync(0xffffffffu, ok)) {
-            aborted = true;
-            break;
-        }
-        const uint4 va = lds128_at<0>(wptr);
-        const uint4 vb = lds128_at<512>(wptr);
+    int units_left = n_units;
+    // one unit of the stage at wptr: UB = 0 for the first unit of the pair, 1 for the second (constant offsets)
+    auto unit = [&](auto ub) {
+        constexpr int WO = decltype(ub)::value * SLAB_UNIT_BYTES;
+        constexpr int XO = decltype(ub)::value * 256;
+        const uint4 va = lds128_at<WO>(wptr);
+        const uint4 vb = lds128_at<WO + 512>(wptr);
         const uint32_t cptr = wptr + cst_off;
-        const ZeroScale<BF16> za = slab_consts<BF16>(lds32_at<0>(cptr));
-        const ZeroScale<BF16> zb = slab_consts<BF16>(lds32_at<32>(cptr));
+        const ZeroScale<BF16> za = slab_consts<BF16>(lds32_at<WO>(cptr));
+        const ZeroScale<BF16> zb = slab_consts<BF16>(lds32_at<WO + 32>(cptr));
         const uint32_t wa[4] = {va.x, va.y, va.z, va.w};
         const uint32_t wb[4] = {vb.x, vb.y, vb.z, vb.w};
         uint32_t xptr[MT];
@@ -383,7 +394,7 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
             dequant8<BF16>(wb[j], zb, pb);
 #pragma unroll
             for (int nt = 0; nt < MT; ++nt) {
-                const uint4 xb = lds128_at<j * 64>(xptr[nt]);
+                const uint4 xb = lds128_at<XO + j * 64>(xptr[nt]);
                 mma_16816<BF16>(acc[nt][0], pa[0], pb[0], pa[1], pb[1], xb.x, xb.y);
                 mma_16816<BF16>(acc[nt][1], pa[2], pb[2], pa[3], pb[3], xb.z, xb.w);
             }
@@ -392,23 +403,9 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
         step(std::integral_constant<int, 1>{});
         step(std::integral_constant<int, 2>{});
         step(std::integral_constant<int, 3>{});
-        // The stage is refilled by the copy engine (async proxy) once the four warps have released it, and the
-        // reads above went through the generic proxy: the proxy fence orders them before the release. Without it the
-        // last activation read of a step was observed to return the refill's data (thread blocks that start while
-        // the memory system is lightly loaded, where a refill lands within a few hundred nanoseconds).
-        fence_proxy_async_shared();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_at<8>(fbar);  // the stage's empty barrier sits right behind its full barrier
-        wptr += stage_bytes;
-        fbar += 16u;
-        if (++s == p.depth) {
-            s = 0;
-            ph ^= 1u;
-            wptr -= ring_bytes;
-            fbar -= bars_bytes;
-        }
-        ++c;
-        if (--seg_left == 0) {
+    };
+    // end of this block's share of a row block (or of its range)
+    auto end_segment = [&]() {
             // end of this block's share of row block b
             float v[MT][4];
 #pragma unroll
@@ -447,7 +444,41 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
                 ++b;
             }
             c_lo = c;
-            seg_left = min(p.chunks - c, n_units - 1 - it);
+            seg_left = min(p.chunks - c, units_left);
+    };
+
+#pragma unroll 1
+    for (int ip = 0; ip < n_pairs; ++ip) {
+        bool ok = mbar_try_wait(fbar, ph) != 0;
+        if (!ok) ok = mbar_wait(fbar, ph, abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) {
+            aborted = true;
+            break;
+        }
+        unit(std::integral_constant<int, 0>{});
+        ++c;
+        --units_left;
+        if (--seg_left == 0) end_segment();
+        if (units_left > 0) {
+            unit(std::integral_constant<int, 1>{});
+            ++c;
+            --units_left;
+            if (--seg_left == 0) end_segment();
+        }
+        // The stage is refilled by the copy engine (async proxy) once the four warps have released it, and the
+        // reads above went through the generic proxy: the proxy fence orders them before the release. Without it the
+        // last activation read of a step was observed to return the refill's data (thread blocks that start while
+        // the memory system is lightly loaded, where a refill lands within a few hundred nanoseconds).
+        fence_proxy_async_shared();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_at<8>(fbar);  // the stage's empty barrier sits right behind its full barrier
+        wptr += stage_bytes;
+        fbar += 16u;
+        if (++s == p.depth) {
+            s = 0;
+            ph ^= 1u;
+            wptr -= ring_bytes;
+            fbar -= bars_bytes;
         }
     }
 
@@ -669,7 +700,7 @@ int launch_slab_unpack(qf_ctx *ctx, int64_t N, int64_t K, const void *blob, void
 // host side
 // ---------------------------------------------------------------------------------------------
 static size_t slab_smem_bytes(int depth, int m_pad) {
-    return (size_t)depth * (SLAB_UNIT_BYTES + m_pad * SLAB_X_PITCH) + 2 * (size_t)depth * 8 + 128 /*alignment*/;
+    return (size_t)depth * (2 * SLAB_UNIT_BYTES + m_pad * SLAB_X_PITCH) + 2 * (size_t)depth * 8 + 128 /*alignment*/;
 }
 
 int slab_m_pad(int64_t M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : M <= 16 ? 16 : 32; }
@@ -685,7 +716,7 @@ void slab_geometry(int64_t M, int64_t N, int64_t K, int sm_count, int grid_reque
     const int env_depth = e_depth ? std::atoi(e_depth) : 0;
     const long long units = (N / 64) * (K / 128);
     const int m_pad = slab_m_pad(M);
-    const size_t stage = SLAB_UNIT_BYTES + (size_t)m_pad * SLAB_X_PITCH;
+    const size_t stage = 2 * SLAB_UNIT_BYTES + (size_t)m_pad * SLAB_X_PITCH;  // a pair of units
     // Measured on B200 (M = 1, bf16, CUDA-graph replays on weights that are not in L2; us per launch):
     //   8.4 MB:  2 blocks/SM 5.7-5.8, 3: 6.8-7.0, 4: 7.3-7.4      30 MB: 2: 12.1-14.7, 3: 12.5-13.3, 4: 11.5-12.3
     //   42 MB:   2: 15.9-19.7, 4: 14.8-15.2                        235 MB: 1: 114, 2: 76-92, 3: 68-79, 4: 65.5
@@ -705,10 +736,13 @@ void slab_geometry(int64_t M, int64_t N, int64_t K, int sm_count, int grid_reque
     }
     if (grid > units) grid = units;
     long long depth = (long long)((200u << 10) / ctas / stage);
-    const long long per_max = (units + grid - 1) / grid;
+    const long long per_max = ((units + grid - 1) / grid + 1) / 2;  // pairs a thread block streams
     if (depth > per_max) depth = per_max;
     if (depth > SLAB_MAX_DEPTH) depth = SLAB_MAX_DEPTH;
-    if (depth > 6) depth = 6;  // deeper rings measured equal or slower; shallow ones leave room on the SM
+    // stages hold pairs of units; deeper rings measured equal or slower, shallow ones leave room on the SM
+    // (30 MB: 3 stages 12.1 us, 4: 12.4, 5: 13.0; 235 MB: 59.5 / 59.1 / 59.1)
+    const long long cap = wbytes <= (64ll << 20) ? 3 : 4;
+    if (depth > cap) depth = cap;
     if (env_depth > 0) depth = env_depth;
     if (depth < 1) depth = 1;
     while (depth > 1 && slab_smem_bytes((int)depth, m_pad) > (size_t)(220u << 10)) --depth;
@@ -721,6 +755,11 @@ size_t slab_workspace_bytes(int grid, int64_t M) {
     return (size_t)grid * 4 * mt * 128 * sizeof(unsigned long long);
 }
 
+static bool slab_fixed_carveout() {
+    const char *e = std::getenv("QF_SLAB_CARVEOUT");  // "0": leave the split to the driver (measurement)
+    return !(e && e[0] == '0');
+}
+
 template <bool BF16, int MT>
 static cudaError_t slab_set_attr() {
     cudaError_t e = cudaFuncSetAttribute(gemv_slab_kernel<BF16, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -728,6 +767,18 @@ static cudaError_t slab_set_attr() {
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(gemv_slab_exch_kernel<BF16, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)(220u << 10));
+    // One shared-memory / L1 split for every launch of these kernels, whatever ring a launch asks for: the kernels
+    // of a decode step follow each other under programmatic dependent launch, and thread blocks of the next kernel
+    // only become resident beside the current one's if the SM does not have to be reconfigured in between (a
+    // 70B-shaped step whose launches alternated between two splits ran 12 % slower than with one). The kernels
+    // barely use L1: weights and activations arrive through bulk copies into shared memory.
+    if (e == cudaSuccess && slab_fixed_carveout()) {
+        e = cudaFuncSetAttribute(gemv_slab_kernel<BF16, MT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 (int)cudaSharedmemCarveoutMaxShared);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemv_slab_exch_kernel<BF16, MT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     (int)cudaSharedmemCarveoutMaxShared);
+    }
     return e;
 }
 
