@@ -238,6 +238,11 @@ def _worker(rank, world, port, out):
         import quantforge_b200 as qf
         from oracle import qf_oracle as O
         from quantforge_b200 import tp
+        # The ranks of this test are separate Python processes that prepare every case on the host (inputs, the CPU
+        # oracle) before they launch; with eight of them sharing the host cores they drift apart by more than the
+        # default limit of a wait for a peer (about a second). A longer limit and a barrier before each case keep a
+        # slow host from reading as a lost peer; the time-out path has its own test.
+        os.environ["QF_EXCHANGE_WAIT_MS"] = "10000"
         comm = qf.Comm(64 * 4096, device=dev)
         res = []
         # every shape shards for 2, 4 and 8 ranks (K/world a multiple of 128, N/world of 16; of 64 where slab is set)
@@ -262,6 +267,8 @@ def _worker(rank, world, port, out):
                                               comm=comm, prepack=prepack, slab=slab)
             x = _t(d["x"], dev, tdt)
             want = O.w4a16_linear(d["x"], d["qweight"], d["scales"], d["zeros"], 128, act, O.F32, accumulate="f64")
+            torch.cuda.synchronize()
+            dist.barrier()
             for _ in range(3):
                 y = lin(x, torch.float32)
             torch.cuda.synchronize()
