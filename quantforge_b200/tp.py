@@ -34,6 +34,13 @@ def check_shardable(N: int, K: int, group_size: int, world: int, mode: str) -> N
         raise ValueError(mode)
 
 
+def _own(t: torch.Tensor) -> torch.Tensor:
+    """A shard in storage of its own. A slice of whole rows is already contiguous, so `.contiguous()` would hand back
+    a view that starts in the middle of the parent's storage - for packed zero points with N/2 bytes per group at an
+    address that is not a multiple of 16 whenever N is not a multiple of 32, which the kernels refuse."""
+    return t.clone(memory_format=torch.contiguous_format)
+
+
 def shard_column(qweight, scales, zeros, rank: int, world: int):
     """-> (qweight[N_r, :], scales[:, N_r], zeros[:, N_r]) for the column-parallel shard of `rank`."""
     N = qweight.shape[0]
@@ -42,9 +49,8 @@ def shard_column(qweight, scales, zeros, rank: int, world: int):
     n0, n1 = rank * N // world, (rank + 1) * N // world
     z = None
     if zeros is not None:
-        z = zeros[:, n0 // 8:n1 // 8] if zeros.dtype == torch.int32 else zeros[:, n0:n1]
-        z = z.contiguous()
-    return qweight[n0:n1].contiguous(), scales[:, n0:n1].contiguous(), z
+        z = _own(zeros[:, n0 // 8:n1 // 8] if zeros.dtype == torch.int32 else zeros[:, n0:n1])
+    return _own(qweight[n0:n1]), _own(scales[:, n0:n1]), z
 
 
 def shard_row(qweight, scales, zeros, rank: int, world: int):
@@ -56,8 +62,8 @@ def shard_row(qweight, scales, zeros, rank: int, world: int):
     g = K // G
     check_shardable(N, K, g, world, "row")
     k0, k1 = rank * K // world, (rank + 1) * K // world
-    z = zeros[k0 // g:k1 // g].contiguous() if zeros is not None else None
-    return qweight[:, k0 // per:k1 // per].contiguous(), scales[k0 // g:k1 // g].contiguous(), z
+    z = _own(zeros[k0 // g:k1 // g]) if zeros is not None else None
+    return _own(qweight[:, k0 // per:k1 // per]), _own(scales[k0 // g:k1 // g]), z
 
 
 class ColumnParallelLinear:

@@ -112,3 +112,24 @@ def test_shard_shape_rules():
     assert a.shape == (32, 128) and b.shape == (2, 32) and c.shape == (2, 4)
     a, b, c = tp.shard_row(qw, sc, z, 1, 2)
     assert a.shape == (64, 64) and b.shape == (1, 64) and c.shape == (1, 8)
+
+
+def test_every_shard_starts_on_a_16_byte_boundary():
+    """The kernels refuse device pointers that are not 16-byte aligned. A row-parallel shard is a slice of whole rows
+    of the scales / zero-point tables; with N = 528 a row of packed zero points is 264 bytes, so a view of the parent
+    would start off the boundary on every odd rank of eight."""
+    from quantforge_b200 import tp
+    N, K, g = 528, 1024, 128
+    qweight = torch.zeros(N, K // 2, dtype=torch.int8)
+    scales = torch.zeros(K // g, N, dtype=torch.float16)
+    zeros = torch.zeros(K // g, N // 8, dtype=torch.int32)
+    for world in (2, 4, 8):
+        for rank in range(world):
+            for t in tp.shard_row(qweight, scales, zeros, rank, world):
+                assert t.data_ptr() % 16 == 0 and t.is_contiguous()
+    qweight = torch.zeros(384, K // 2, dtype=torch.int8)
+    scales = torch.zeros(K // g, 384, dtype=torch.float16)
+    zeros = torch.zeros(K // g, 384 // 8, dtype=torch.int32)
+    for rank in range(8):
+        for t in tp.shard_column(qweight, scales, zeros, rank, 8):
+            assert t.data_ptr() % 16 == 0 and t.is_contiguous()
