@@ -373,6 +373,8 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
     }
 
     int units_left = n_units;
+    int seg_len = seg_left;                                   // units of the current row-block segment
+    const int odd_tail = (n_units & 1) ? n_pairs - 1 : -1;   // the pair that holds a single unit
     // one unit of the stage at wptr: UB = 0 for the first unit of the pair, 1 for the second (constant offsets)
     auto unit = [&](auto ub) {
         constexpr int WO = decltype(ub)::value * SLAB_UNIT_BYTES;
@@ -406,6 +408,8 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
     };
     // end of this block's share of a row block (or of its range)
     auto end_segment = [&]() {
+            c += seg_len;
+            units_left -= seg_len;
             // end of this block's share of row block b
             float v[MT][4];
 #pragma unroll
@@ -444,7 +448,8 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
                 ++b;
             }
             c_lo = c;
-            seg_left = min(p.chunks - c, units_left);
+            seg_len = min(p.chunks - c, units_left);
+            seg_left = seg_len;
     };
 
 #pragma unroll 1
@@ -456,13 +461,9 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
             break;
         }
         unit(std::integral_constant<int, 0>{});
-        ++c;
-        --units_left;
         if (--seg_left == 0) end_segment();
-        if (units_left > 0) {
+        if (ip != odd_tail) {
             unit(std::integral_constant<int, 1>{});
-            ++c;
-            --units_left;
             if (--seg_left == 0) end_segment();
         }
         // The stage is refilled by the copy engine (async proxy) once the four warps have released it, and the
