@@ -102,8 +102,11 @@ __device__ __forceinline__ long long slab_cta_of(long long u, long long U, long 
 template <bool BF16>
 __device__ __forceinline__ ZeroScale<BF16> slab_consts(uint32_t word) {
     ZeroScale<BF16> zs;
-    zs.zsub = prmt(word, word, 0x1010u);
-    zs.s2 = prmt(word, word, 0x3232u);
+    // low half / high half broadcast, written as register pack / unpack so that the assembler may fold the
+    // broadcast into the operand selectors of the packed-half instructions that consume it
+    asm("{.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tmov.b32 %0, {lo, lo};\n\tmov.b32 %1, {hi, hi};}"
+        : "=r"(zs.zsub), "=r"(zs.s2)
+        : "r"(word));
     // f16 only: -(64 + z) = (1024 + z) * (-1) + 960, exact in f16
     zs.zfma = BF16 ? 0u : fma_f16x2(zs.zsub, 0xbc00bc00u, 0x63806380u);
     return zs;
@@ -454,11 +457,12 @@ __device__ __forceinline__ void gemv_slab_body(const SlabParams &p, const typena
 
 #pragma unroll 1
     for (int ip = 0; ip < n_pairs; ++ip) {
-        bool ok = mbar_try_wait(fbar, ph) != 0;
-        if (!ok) ok = mbar_wait(fbar, ph, abort_flag);
-        if (!__all_sync(0xffffffffu, ok)) {
-            aborted = true;
-            break;
+        if (!__all_sync(0xffffffffu, mbar_try_wait(fbar, ph) != 0)) {
+            // not there yet for some lane: everybody takes the bounded wait
+            if (!__all_sync(0xffffffffu, mbar_wait(fbar, ph, abort_flag))) {
+                aborted = true;
+                break;
+            }
         }
         unit(std::integral_constant<int, 0>{});
         if (--seg_left == 0) end_segment();
