@@ -67,6 +67,10 @@ def test_prepack_is_a_permutation_of_the_codes():
     (17, 1024, 256, "bf16", 128, "i8", 0),       # four batch tiles, ragged
     (32, 4096, 256, "bf16", 128, "u4", 0),
     (1, 8192, 1280, "bf16", 128, "u4", 0),       # a tensor-parallel shard of a 70B q/k/v projection
+    (3, 128, 512, "bf16", 128, "u4", 0),         # one K chunk per row block: every pair of units spans two row blocks
+    (1, 128, 512, "f16", 128, "i8", 3),          # the same with ranges of 3, 3 and 2 units (an odd tail)
+    (2, 384, 192, "f16", 128, "u4", 2),          # three chunks per row block: pairs straddle a row block every time
+    (1, 640, 320, "bf16", 128, "u4", 7),         # 25 units over 7 thread blocks: odd and even ranges, odd chunk count
 ])
 def test_slab_linear_matches_oracle(M, K, N, act, group, zmode, grid):
     import quantforge_b200 as qf
