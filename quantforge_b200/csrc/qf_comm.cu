@@ -188,7 +188,7 @@ static int linear_exchange(qf_ctx *ctx, qf_comm *comm, const qf_linear_desc *des
         // launch must be resident at once on every rank: an explicit grid of whole multiples of the SM count (the
         // launch checks it against the occupancy the kernel really gets). Same size rule as the plain kernel.
         const long long wbytes = (long long)(local_desc.N / 64) * (local_desc.K / 128) * QF_SLAB_UNIT_BYTES;
-        const int per_sm = (wbytes <= (16ll << 20)) ? 2 : (local_desc.M > 16 ? 3 : 4);
+        const int per_sm = (wbytes <= kSlabSmallBytes) ? 2 : (local_desc.M > 16 ? 3 : 4);
         local_desc.split_k = per_sm * ctx->sm_count;
         desc = &local_desc;
     }

@@ -221,6 +221,11 @@ int gemv_init(qf_ctx *ctx);
 int gemm_init(qf_ctx *ctx);
 // streaming GEMV on QF_LAYOUT_GEMV_SLAB weights (qf_gemv_slab.cu)
 int gemv_slab_init(qf_ctx *ctx);
+// Blobs up to this size run with two thread blocks per SM, larger ones with four (see slab_geometry). Launched
+// alone, matrices up to about 34 MB are faster with two (17 MB: 7.0 vs 8.4 us); inside a decode step, where the
+// neighbours are kernels of other sizes, a limit of 36 MB measured no better than 16 MB (5.84 vs 5.79 ms per
+// token on two GPUs), so the limit stays where the step-level numbers were taken.
+constexpr long long kSlabSmallBytes = 16ll << 20;
 int slab_m_pad(int64_t M);
 void slab_geometry(int64_t M, int64_t N, int64_t K, int sm_count, int grid_request, int *grid_out, int *depth_out);
 size_t slab_workspace_bytes(int grid, int64_t M);

@@ -722,13 +722,13 @@ void slab_geometry(int64_t M, int64_t N, int64_t K, int sm_count, int grid_reque
     const long long units = (N / 64) * (K / 128);
     const int m_pad = slab_m_pad(M);
     const size_t stage = 2 * SLAB_UNIT_BYTES + (size_t)m_pad * SLAB_X_PITCH;  // a pair of units
-    // Measured on B200 (M = 1, bf16, CUDA-graph replays on weights that are not in L2; us per launch):
-    //   8.4 MB:  2 blocks/SM 5.7-5.8, 3: 6.8-7.0, 4: 7.3-7.4      30 MB: 2: 12.1-14.7, 3: 12.5-13.3, 4: 11.5-12.3
-    //   42 MB:   2: 15.9-19.7, 4: 14.8-15.2                        235 MB: 1: 114, 2: 76-92, 3: 68-79, 4: 65.5
+    // Measured on B200 (M = 1, bf16, CUDA-graph replays on weights that are not in L2; us per launch, 2 / 3 / 4
+    // blocks per SM):   8.4 MB 4.8 / 6.0 / 6.2    17 MB 7.0 / 8.3 / 8.4    21 MB 8.3 / 10.1 / 9.8    29 MB 10.4 / 11.8 / 10.8
+    //                   34 MB 11.3 / 13.1 / 11.5   42 MB 13.6 / 15.5 / 12.8  59 MB 17.9 / 20.5 / 16.4   235 MB 64 / 73 / 55.5
     // Large matrices want every warp slot streaming; small ones want room left on the SM, so that the next kernel of
     // the stream (programmatic dependent launch) is resident with its weights already in flight when this one ends.
     const long long wbytes = units * SLAB_UNIT_BYTES;
-    int ctas = wbytes <= (16ll << 20) ? 2 : 4;
+    int ctas = wbytes <= kSlabSmallBytes ? 2 : 4;
     if (m_pad > 16) ctas = std::min(ctas, 3);  // register budget of the four-batch-tile instantiation
     while (ctas > 1 && units / ((long long)sm_count * ctas) < 2) --ctas;
     if (env_ctas > 0) ctas = env_ctas;
